@@ -10,10 +10,15 @@ layers that keep every key and layers that keep a window do not share storage.
 Storage of a group: ``pages[entry, page, 0|1, kv_head, token(64), channel]``
 (keys at 0, values at 1; a request with ``planes=1`` has the key plane only and
 its view hands out the key plane as the value plane too: a mixer whose values
-are a part of what it stores as keys).  ``block_table[slot, i]`` is the page holding tokens
+are a part of what it stores as keys).  A request whose values have a size of
+their own (``value_dim``) keeps, per page, the key block ``[kv_head, 64,
+head_dim]`` and behind it the value block ``[kv_head, 64, value_dim]``; both
+planes still share one page stride and one block table.  ``block_table[slot, i]`` is the page holding tokens
 ``[64*i, 64*i+64)`` of the sequence in `slot`.  A sequence holds
 ceil(length/64) pages per group -- a group that keeps a window gives back, as
-the sequence grows, the pages that have slid out of it -- and pages and the
+the sequence grows, the pages that have slid out of it; a group whose keys are seen
+within stretches of ``chunk`` positions gives back the pages that lie wholly
+before the stretch of the next token -- and pages and the
 slot return to the free lists when the sequence is closed, and are handed out
 again.
 
@@ -40,6 +45,24 @@ class KVRequest:
     head_dim: int
     window: Optional[int] = None      # None: every key is kept
     planes: int = 2                   # 2: keys and values; 1: keys only (the values are a part of the key rows)
+    value_dim: Optional[int] = None   # channels of a stored value; None: head_dim
+    chunk: Optional[int] = None       # keys are seen within stretches of so many positions (None: not)
+
+    @property
+    def first_needed(self):
+        """A function of the next token's position: the first position it still sees."""
+        def lo(position: int) -> int:
+            first = 0
+            if self.window is not None:
+                first = max(first, position - self.window + 1)
+            if self.chunk is not None:
+                first = max(first, position - position % self.chunk)
+            return first
+        return lo
+
+    @property
+    def forgets(self) -> bool:
+        return self.window is not None or self.chunk is not None
 
 
 @dataclass(frozen=True)
@@ -56,10 +79,12 @@ _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": 
 class KVEntryView:
     """What a kernel needs to address one run's keys and values."""
     __slots__ = ("k", "v", "page_stride", "block_table", "table_stride", "n_kv_heads", "head_dim",
-                 "window")
+                 "window", "value_dim", "chunk")
 
-    def __init__(self, k, v, block_table, n_kv_heads, head_dim, window):
+    def __init__(self, k, v, block_table, n_kv_heads, head_dim, window, value_dim=None, chunk=None):
         self.k, self.v = k, v
+        self.value_dim = head_dim if value_dim is None else value_dim     # width of a row of the value plane
+        self.chunk = chunk
         self.page_stride = k.stride(0)
         self.block_table = block_table
         self.table_stride = block_table.stride(0)
@@ -87,8 +112,16 @@ class _KVGroup:
         self.pool = PagePool(n_pages)
         if request.planes not in (1, 2):
             raise ValueError(f"a key/value store has 1 or 2 planes, not {request.planes}")
-        self.storage = torch.zeros((n_entries, n_pages, request.planes, request.n_kv_heads, PAGE_TOKENS,
-                                    request.head_dim), dtype=dtype, device=device)
+        self.value_dim = request.head_dim if request.value_dim is None else int(request.value_dim)
+        if self.value_dim != request.head_dim:
+            if request.planes != 2:
+                raise ValueError("values of a size of their own need a value plane")
+            # per page: the key block, then the value block
+            self.storage = torch.zeros((n_entries, n_pages, request.n_kv_heads * PAGE_TOKENS *
+                                        (request.head_dim + self.value_dim)), dtype=dtype, device=device)
+        else:
+            self.storage = torch.zeros((n_entries, n_pages, request.planes, request.n_kv_heads, PAGE_TOKENS,
+                                        request.head_dim), dtype=dtype, device=device)
         self.table_host = torch.zeros((n_slots, pages_per_seq), dtype=torch.int32)
         if device.type == "cuda":
             self.table_host = self.table_host.pin_memory()
@@ -98,8 +131,14 @@ class _KVGroup:
 
     def view(self, entry: int) -> KVEntryView:
         s = self.storage[entry]
-        return KVEntryView(s[:, 0], s[:, self.request.planes - 1], self.table, self.request.n_kv_heads,
-                           self.request.head_dim, self.request.window)
+        r = self.request
+        if self.value_dim != r.head_dim:
+            split = r.n_kv_heads * PAGE_TOKENS * r.head_dim
+            k = s[:, :split].view(s.shape[0], r.n_kv_heads, PAGE_TOKENS, r.head_dim)
+            v = s[:, split:].view(s.shape[0], r.n_kv_heads, PAGE_TOKENS, self.value_dim)
+            return KVEntryView(k, v, self.table, r.n_kv_heads, r.head_dim, r.window, self.value_dim, r.chunk)
+        return KVEntryView(s[:, 0], s[:, r.planes - 1], self.table, r.n_kv_heads, r.head_dim, r.window,
+                           self.value_dim, r.chunk)
 
 
 class Cache:
@@ -246,14 +285,14 @@ class Cache:
                 raise CacheMisuse(f"slot {slot} advanced to {new_length} tokens without reserved pages")
         self._length[slot] = new_length
         # A group that keeps a window gives back the pages no later token can see: the next
-        # token, at position new_length, reaches back to new_length - window + 1.  Their
+        # token, at position new_length, reaches back to new_length - window + 1 (to the
+        # start of its stretch, for keys seen within stretches).  Their
         # table entries stay as they are; no kernel reads a page before a window's first.
         for grp in self.groups:
-            window = grp.request.window
-            if window is None:
+            if not grp.request.forgets:
                 continue
             have = grp.pages_of[slot]
-            gone = [i for i in range(min(len(have), max(0, new_length - window + 1) // PAGE_TOKENS)) if have[i] >= 0]
+            gone = [i for i in range(min(len(have), grp.request.first_needed(new_length) // PAGE_TOKENS)) if have[i] >= 0]
             if gone:
                 grp.pool.free([have[i] for i in gone], slot)
                 for i in gone:
@@ -272,11 +311,10 @@ class Cache:
         if not 0 <= new_length <= self._length[slot]:
             raise CacheMisuse(f"cannot truncate slot {slot} from {self._length[slot]} to {new_length}")
         for grp in self.groups:
-            window = grp.request.window
-            if window is not None and any(p < 0 for p in grp.pages_of[slot][max(0, new_length - window + 1) // PAGE_TOKENS:
+            if grp.request.forgets and any(p < 0 for p in grp.pages_of[slot][grp.request.first_needed(new_length) // PAGE_TOKENS:
                                                                          (new_length + PAGE_TOKENS - 1) // PAGE_TOKENS]):
                 raise CacheMisuse(f"slot {slot} cannot go back to {new_length} tokens: a layer that keeps a window "
-                                  f"of {window} keys has given back pages that length would need")
+                                  f"or a stretch of keys has given back pages that length would need")
         self._length[slot] = new_length
 
     def flush_tables(self) -> None:

@@ -1,0 +1,120 @@
+// What stands between the fused projection of an attention mixer and the
+// attention itself, for mixers whose projections have more to them than a
+// rotation: one block per token takes the projection's float sums
+//   [ q: n_heads x hd | k: n_kv x hd | v: n_kv x vd | g: n_heads ]
+// and, all in float,
+//   * adds the biases of q, k and v;
+//   * rotates the first `rot` channels of every query and key head, channel i with
+//     i + rot/2, by the token's (cos, sin) table; the rest of a head passes;
+//   * with `unit_norm`, divides every rotated query and key head by its root mean
+//     square, x / sqrt(mean(x^2) + eps);
+//   * blends the values with those an earlier layer left for the step,
+//     v <- (1 - lambda) v + lambda v_first, or leaves its own for later layers;
+//   * turns the gate columns into sigmoid factors, one per query head;
+// then rounds once: queries to `q_out`, keys and values into the token's place in
+// the paged cache (key rows of hd, value rows of vd channels).
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_finish_kernel(const float* __restrict__ sums, int ld, const float* __restrict__ bias,
+                  const float2* __restrict__ cos_sin, int rot, int unit_norm, float eps,
+                  const float* __restrict__ v_first, float* __restrict__ v_keep, float lambda,
+                  T* __restrict__ q_out, int ldq, float* __restrict__ gate_out,
+                  T* __restrict__ kc, T* __restrict__ vc, long long page_stride,
+                  const int* __restrict__ block_table, int table_stride,
+                  const int* __restrict__ token_seq, const int* __restrict__ slots,
+                  const int* __restrict__ positions,
+                  int n_heads, int n_kv, int hd, int vd, int has_gate) {
+    chain_release();
+    chain_wait();
+    extern __shared__ float row[];
+    const int n = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const int q_w = n_heads * hd, k_w = n_kv * hd, v_w = n_kv * vd;
+    const int biased = q_w + k_w + v_w;
+    const int width = biased + (has_gate ? n_heads : 0);
+    const float* src = sums + (size_t)n * ld;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = src[i] + ((bias && i < biased) ? bias[i] : 0.f);
+    __syncthreads();
+
+    const int pos = positions[n];
+    size_t page_off = 0;
+    if (kc) {
+        const int slot = slots[token_seq[n]];
+        page_off = (size_t)block_table[(size_t)slot * table_stride + pos / kPageTokens] * page_stride;
+    }
+    const int rhalf = rot >> 1;
+    // queries and keys: a warp a head
+    for (int head = warp; head < n_heads + n_kv; head += n_warps) {
+        float* x = row + (size_t)head * hd;
+        if (cos_sin) {
+            for (int i = lane; i < rhalf; i += 32) {
+                const float2 cs = cos_sin[(size_t)n * rhalf + i];
+                const float a = x[i], b = x[i + rhalf];
+                x[i] = a * cs.x - b * cs.y;
+                x[i + rhalf] = b * cs.x + a * cs.y;
+            }
+            __syncwarp();
+        }
+        float inv = 1.f;
+        if (unit_norm) {
+            float sq = 0.f;
+            for (int i = lane; i < hd; i += 32) sq = fmaf(x[i], x[i], sq);
+            inv = 1.0f / sqrtf(warp_sum(sq) / (float)hd + eps);
+        }
+        T* dst;
+        if (head < n_heads) dst = q_out + (size_t)n * ldq + (size_t)head * hd;
+        else if (kc) dst = kc + page_off + ((size_t)(head - n_heads) * kPageTokens + (pos % kPageTokens)) * hd;
+        else continue;
+        for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(x[i] * inv);
+    }
+    // values
+    const float* v = row + q_w + k_w;
+    for (int i = threadIdx.x; i < v_w; i += blockDim.x) {
+        float val = v[i];
+        if (v_keep) v_keep[(size_t)n * v_w + i] = val;
+        if (v_first) val = (1.0f - lambda) * val + lambda * v_first[(size_t)n * v_w + i];
+        if (vc) {
+            const int head = i / vd, c = i - head * vd;
+            vc[page_off + ((size_t)head * kPageTokens + (pos % kPageTokens)) * vd + c] = from_f32<T>(val);
+        }
+    }
+    if (has_gate)
+        for (int h = threadIdx.x; h < n_heads; h += blockDim.x)
+            gate_out[(size_t)n * n_heads + h] = 1.0f / (1.0f + expf(-row[biased + h]));
+}
+}  // namespace
+
+GTG_API int gtg_qkv_finish(int dtype, const float* sums, int ld, const float* bias, const float* cos_sin, int rot,
+                           int unit_norm, float eps, const float* v_first, float* v_keep, float lambda,
+                           void* q_out, int ldq, float* gate_out, void* kc, void* vc, long long page_stride,
+                           const int* block_table, int table_stride, const int* token_seq, const int* slots,
+                           const int* positions, int N, int n_heads, int n_kv, int hd, int vd, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (n_heads <= 0 || n_kv <= 0 || hd <= 0 || vd <= 0 || rot < 0 || (rot & 1) || rot > hd) return kErrBadArgument;
+    if ((cos_sin != nullptr) != (rot > 0) || (kc == nullptr) != (vc == nullptr)) return kErrBadArgument;
+    const int has_gate = gate_out != nullptr;
+    const int width = n_heads * hd + n_kv * (hd + vd) + (has_gate ? n_heads : 0);
+    if (ld < width) return kErrBadArgument;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return kErrUnsupported;
+#define GTG_FINISH(T)                                                                                              \
+    do {                                                                                                           \
+        auto kernel = qkv_finish_kernel<T>;                                                                        \
+        if (smem > 48 * 1024) {                                                                                    \
+            const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                                   \
+        }                                                                                                          \
+        return launch_chained(kernel, dim3(N), dim3(256), smem, stream, sums, ld, bias, (const float2*)cos_sin, rot, \
+                              unit_norm, eps, v_first, v_keep, lambda, (T*)q_out, ldq, gate_out, (T*)kc, (T*)vc,    \
+                              page_stride, block_table, table_stride, token_seq, slots, positions, n_heads, n_kv,  \
+                              hd, vd, has_gate);                                                                   \
+    } while (0)
+    if (dtype == 0) GTG_FINISH(float);
+    if (dtype == 1) GTG_FINISH(bf16);
+#undef GTG_FINISH
+    return kErrBadArgument;
+}

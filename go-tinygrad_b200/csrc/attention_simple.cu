@@ -2,7 +2,10 @@
 // (token, query head).  This is the attention of the float32 path (and the
 // bfloat16 path's route for head sizes its tiled kernels refuse).  It serves a
 // prompt and a decode step alike: token n at position p sees keys lo..p of its
-// own sequence, lo = 0 or p-window+1.
+// own sequence, lo = 0, or p-window+1 (a sliding window), or the first position
+// of p's chunk, p - p % chunk (chunked attention: positions are cut into
+// stretches of `chunk`, counted from the sequence's start, and a token sees the
+// keys of its own stretch only).
 //
 // Scores are (q.k)*scale with the scale applied after the dot; softmax is the
 // streaming form of max / exp / sum / normalise (model/llama.go:1626-1660), with
@@ -13,7 +16,10 @@
 // `vd` is how many channels a value has: the first vd channels of a row of the
 // value plane (vd = hd for ordinary heads).  A mixer whose values are a leading
 // part of what it stores as keys passes the key plane for both and a smaller vd;
-// the output then has vd channels per head.
+// the output then has vd channels per head.  `vrow` is the width of a row of the
+// value plane (hd when keys and values share a page layout; a cache whose values
+// have a size of their own stores rows of vd channels).  `gate` (or null):
+// float [N, n_heads], a factor on each head's output.
 #include "common.cuh"
 #include <math.h>
 
@@ -29,7 +35,8 @@ attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ token_seq, const int* __restrict__ slots,
                         const int* __restrict__ positions,
-                        int N, int n_heads, int n_kv, int hd, int vd, float scale, int window) {
+                        int N, int n_heads, int n_kv, int hd, int vd, int vrow, float scale, int window, int chunk,
+                        const float* __restrict__ gate) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * kWarps + warp;
@@ -39,7 +46,8 @@ attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
     const int pos = positions[n];
     const int slot = slots[token_seq[n]];
     const int* table = block_table + (size_t)slot * table_stride;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) lo = max(lo, pos - pos % chunk);
 
     float* qs = smem + warp * hd;
     for (int d = lane; d < hd; d += 32) qs[d] = to_f32<T>(q[(size_t)n * ldq + h * hd + d]);
@@ -73,7 +81,7 @@ attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
             const float pj = __shfl_sync(0xffffffffu, p, src);
             const int pg = __shfl_sync(0xffffffffu, page, src);
             const int tj = t0 + src;
-            const T* vp = vc + (size_t)pg * page_stride + ((size_t)kvh * kPageTokens + (tj % kPageTokens)) * hd;
+            const T* vp = vc + (size_t)pg * page_stride + ((size_t)kvh * kPageTokens + (tj % kPageTokens)) * vrow;
 #pragma unroll
             for (int j = 0; j < kMaxPerLane; ++j) {
                 const int d = lane + 32 * j;
@@ -82,7 +90,7 @@ attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
         }
         m = m_new;
     }
-    const float inv = 1.0f / l;
+    const float inv = (gate ? gate[(size_t)n * n_heads + h] : 1.0f) / l;
 #pragma unroll
     for (int j = 0; j < kMaxPerLane; ++j) {
         const int d = lane + 32 * j;
@@ -95,11 +103,11 @@ GTG_API int gtg_attention_simple(int dtype, const void* q, int ldq, void* out, i
                                  const void* kc, const void* vc, long long page_stride,
                                  const int* block_table, int table_stride,
                                  const int* token_seq, const int* slots, const int* positions,
-                                 int N, int n_heads, int n_kv, int hd, int vd, float scale, int window,
-                                 cudaStream_t stream) {
+                                 int N, int n_heads, int n_kv, int hd, int vd, int vrow, float scale, int window, int chunk,
+                                 const float* gate, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || hd <= 0) return kErrBadArgument;
-    if (vd <= 0 || vd > hd) return kErrBadArgument;
+    if (vd <= 0 || vd > vrow || window < 0 || chunk < 0) return kErrBadArgument;
     if (hd > kMaxHeadDim || vd > 32 * 32) return kErrUnsupported;
     const long long warps = (long long)N * n_heads;
     const long long blocks = (warps + kWarps - 1) / kWarps;
@@ -108,7 +116,7 @@ GTG_API int gtg_attention_simple(int dtype, const void* q, int ldq, void* out, i
 #define GTG_SIMPLE(T, PER)                                                                                   \
     attention_simple_kernel<T, PER><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(                            \
         (const T*)q, ldq, (T*)out, ldo, (const T*)kc, (const T*)vc, page_stride, block_table, table_stride,      \
-        token_seq, slots, positions, N, n_heads, n_kv, hd, vd, scale, window)
+        token_seq, slots, positions, N, n_heads, n_kv, hd, vd, vrow, scale, window, chunk, gate)
     if (dtype == 0) {
         if (vd <= 256) GTG_SIMPLE(float, 8); else if (vd <= 512) GTG_SIMPLE(float, 16); else GTG_SIMPLE(float, 32);
     } else if (dtype == 1) {

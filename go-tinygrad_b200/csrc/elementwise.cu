@@ -7,12 +7,12 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// out[n,:] = table[tokens[n],:] widened to float (the residual stream).  No
-// scaling (model/inference_helpers.go:9-34).  Token ids are validated by the
+// out[n,:] = table[tokens[n],:] widened to float (the residual stream), times
+// `scale` (1: no scaling, as in model/inference_helpers.go:9-34).  Token ids are validated by the
 // host; an id outside the table is clamped so the kernel never reads outside.
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                             float* __restrict__ out, int H, int V) {
+                             float* __restrict__ out, int H, int V, float scale) {
     chain_wait();        // the step's metadata is written here or just before: nothing later may start early
     chain_release();
     const int n = blockIdx.x;
@@ -20,16 +20,16 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
     tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
     const T* src = table + (size_t)tok * H;
     float* dst = out + (size_t)n * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<T>(src[i]) * scale;
 }
 
 GTG_API int gtg_embed(int dtype, const int* tokens, const void* table, float* out,
-                      int N, int H, int V, cudaStream_t stream) {
+                      int N, int H, int V, float scale, cudaStream_t stream) {
     int st = 0;
     if (N <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
-    if (dtype == 0) st = launch_chained(embed_kernel<float>, dim3(N), dim3(threads), 0, stream, tokens, (const float*)table, out, H, V);
-    else if (dtype == 1) st = launch_chained(embed_kernel<bf16>, dim3(N), dim3(threads), 0, stream, tokens, (const bf16*)table, out, H, V);
+    if (dtype == 0) st = launch_chained(embed_kernel<float>, dim3(N), dim3(threads), 0, stream, tokens, (const float*)table, out, H, V, scale);
+    else if (dtype == 1) st = launch_chained(embed_kernel<bf16>, dim3(N), dim3(threads), 0, stream, tokens, (const bf16*)table, out, H, V, scale);
     else return kErrBadArgument;
     return st;
 }

@@ -4,7 +4,9 @@
 // experts can be recorded as a graph.
 //
 //   route    z = R x + b in float; the `top` largest z (ties: the lower index)
-//            are the token's experts, their weights softmax over those z alone.
+//            are the token's experts, their weights softmax over those z alone
+//            (scoring 0) or each chosen expert's own sigmoid(z), not renormalised
+//            (scoring 1; the largest sigmoid is the largest z).
 //   arrange  item i = (token i / top, its (i % top)-th expert).  Items of one
 //            expert get consecutive rows, every expert's stretch padded to whole
 //            tiles of `tile` rows, so that a tile of rows has one expert:
@@ -15,8 +17,11 @@
 //   product  C[row,:] = A[source(row),:] . W[expert(row)]^T, tiles of 64 rows,
 //            one accumulator per output walking k in order.
 //   gather   G[row,:] = x[token of row_item[row],:] (zeros for padding): the arranged
-//            copy of the inputs that a product fed by tensor copies reads.
-//   combine  out[t,:] = sum_k weight[t,k] * Y[item_row[t*top+k],:], k in order.
+//            copy of the inputs that a product fed by tensor copies reads.  With
+//            weights, G[row,:] = weight[item] * x[token,:], the product in float and
+//            rounded once: a mixture whose weights scale an expert's input.
+//   combine  out[t,:] = sum_k weight[t,k] * Y[item_row[t*top+k],:], k in order
+//            (weights null: the plain sum).
 #include "common.cuh"
 #include <math.h>
 
@@ -28,7 +33,7 @@ namespace {
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, const float* __restrict__ bias,
-                 int* __restrict__ chosen, float* __restrict__ weights, int N, int H, int E, int top) {
+                 int* __restrict__ chosen, float* __restrict__ weights, int N, int H, int E, int top, int scoring) {
     chain_release();
     chain_wait();
     extern __shared__ float smem[];
@@ -74,11 +79,11 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
             z[arg] = __int_as_float(0x7fc00000);
             if (k == 0) best0 = best;
             chosen[(size_t)n * top + k] = arg;
-            const float p = expf(best - best0);
+            const float p = scoring == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - best0);
             xs[k] = p;                                      // the staged row is no longer needed (top <= E <= H is checked)
             total += p;
         }
-        const float inv = 1.0f / total;
+        const float inv = scoring == 1 ? 1.0f : 1.0f / total;
         for (int k = 0; k < top; ++k) weights[(size_t)n * top + k] = xs[k] * inv;
     }
 }
@@ -195,6 +200,23 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ x, int ldx, const int
     for (int i = threadIdx.x; i < H8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0u, 0u, 0u, 0u);
 }
 
+// The same with a weight per item, any type and width: G[row,:] = weights[item] * x[token,:].
+template <typename T>
+__global__ void moe_gather_scaled_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ row_item, int item_div,
+                                         const float* __restrict__ weights, T* __restrict__ out, int H) {
+    chain_release();
+    chain_wait();
+    const int item = row_item[blockIdx.x];
+    T* dst = out + (size_t)blockIdx.x * H;
+    if (item < 0) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = from_f32<T>(0.f);
+        return;
+    }
+    const float w = weights ? weights[item] : 1.0f;
+    const T* src = x + (size_t)(item / item_div) * ldx;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = from_f32<T>(w * to_f32<T>(src[i]));
+}
+
 // ---- combine ----------------------------------------------------------------------
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, int ldy, const int* __restrict__ item_row,
@@ -205,22 +227,22 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int ldy, const i
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top; ++k)
-            s = fmaf(weights[(size_t)t * top + k], y[(size_t)item_row[(size_t)t * top + k] * ldy + i], s);
+            s = fmaf(weights ? weights[(size_t)t * top + k] : 1.0f, y[(size_t)item_row[(size_t)t * top + k] * ldy + i], s);
         out[(size_t)t * H + i] = from_f32<T>(s);
     }
 }
 }  // namespace
 
 GTG_API int gtg_moe_route(int dtype, const void* x, int ldx, const float* router, const float* bias, int* chosen,
-                          float* weights, int N, int H, int E, int top, cudaStream_t stream) {
+                          float* weights, int N, int H, int E, int top, int scoring, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (E <= 0 || top <= 0 || top > E || H <= 0) return kErrBadArgument;
+    if (E <= 0 || top <= 0 || top > E || H <= 0 || scoring < 0 || scoring > 1) return kErrBadArgument;
     if (top > H) return kErrUnsupported;
     const size_t smem = (size_t)(H + E) * sizeof(float);
     if (smem > 48 * 1024) return kErrUnsupported;
     const dim3 grid(N);
-    if (dtype == 0) return launch_chained(moe_route_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, ldx, router, bias, chosen, weights, N, H, E, top);
-    if (dtype == 1) return launch_chained(moe_route_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)x, ldx, router, bias, chosen, weights, N, H, E, top);
+    if (dtype == 0) return launch_chained(moe_route_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, ldx, router, bias, chosen, weights, N, H, E, top, scoring);
+    if (dtype == 1) return launch_chained(moe_route_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)x, ldx, router, bias, chosen, weights, N, H, E, top, scoring);
     return kErrBadArgument;
 }
 
@@ -268,6 +290,16 @@ GTG_API int gtg_moe_gather(const void* x, int ldx, const int* row_item, int item
     if (H <= 0 || item_div <= 0) return kErrBadArgument;
     if (H % 8 || ldx % 8 || ((uintptr_t)x % 16) || ((uintptr_t)out % 16)) return kErrUnsupported;
     return launch_chained(moe_gather_kernel, dim3(rows), dim3(128), 0, stream, (const bf16*)x, ldx, row_item, item_div, (bf16*)out, H / 8);
+}
+
+// out[row, :] = weights[item] * x[item / item_div, :] (weights null: 1), zeros in padding rows; any width.
+GTG_API int gtg_moe_gather_scaled(int dtype, const void* x, int ldx, const int* row_item, int item_div, const float* weights,
+                                  void* out, int rows, int H, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H <= 0 || item_div <= 0) return kErrBadArgument;
+    if (dtype == 0) return launch_chained(moe_gather_scaled_kernel<float>, dim3(rows), dim3(128), 0, stream, (const float*)x, ldx, row_item, item_div, weights, (float*)out, H);
+    if (dtype == 1) return launch_chained(moe_gather_scaled_kernel<bf16>, dim3(rows), dim3(128), 0, stream, (const bf16*)x, ldx, row_item, item_div, weights, (bf16*)out, H);
+    return kErrBadArgument;
 }
 
 GTG_API int gtg_moe_combine(int dtype, const float* y, int ldy, const int* item_row, const float* weights, void* out,

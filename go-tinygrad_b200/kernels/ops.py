@@ -21,7 +21,7 @@ _P, _I, _L, _F, _U, _D = c_void_p, c_int, c_longlong, c_float, c_ulonglong, c_do
 
 # library, symbol -> argument types (the stream is always last)
 _SIGNATURES = {
-    "gtg_embed": ("elementwise", [_I, _P, _P, _P, _I, _I, _I, _P]),
+    "gtg_embed": ("elementwise", [_I, _P, _P, _P, _I, _I, _I, _F, _P]),
     "gtg_add_rmsnorm": ("elementwise", [_I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
     "gtg_swiglu": ("elementwise", [_I, _P, _P, _I, _I, _P]),
     "gtg_rope_table": ("elementwise", [_P, _P, _P, _I, _I, _D, _P]),
@@ -55,7 +55,7 @@ _SIGNATURES = {
     "gtg_gemm_bf16_swapab_scratch_floats": ("gemm_bf16_swapab", [_I, _I, _I]),
     "gtg_gemm_bf16_swapab_status": ("gemm_bf16_swapab", []),
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
-                                                  _I, _I, _I, _I, _I, _F, _I, _P]),
+                                                  _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P]),
     "gtg_rmsnorm_add": ("elementwise", [_I, _I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
     "gtg_round_rows": ("elementwise", [_I, _P, _P, _L, _P]),
     "gtg_swiglu_bias": ("elementwise", [_I, _P, _P, _P, _P, _I, _I, _I, _P]),
@@ -76,7 +76,11 @@ _SIGNATURES = {
     "gtg_latent_attention_splits": ("latent", [_I, _I, _I, _I, _I, _I]),
     "gtg_moe_gather": ("experts", [_P, _I, _P, _I, _P, _I, _I, _P]),
     "gtg_gemm_bf16_tcgen05_grouped": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
-    "gtg_moe_route": ("experts", [_I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "gtg_moe_route": ("experts", [_I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_moe_gather_scaled": ("experts", [_I, _P, _I, _P, _I, _P, _P, _I, _I, _P]),
+    "gtg_hyper_norm": ("hyper", [_I, _I, _P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P]),
+    "gtg_qkv_finish": ("attention_prep", [_I, _P, _I, _P, _P, _I, _I, _F, _P, _P, _F, _P, _I, _P, _P, _P, _L, _P, _I, _P, _P, _P,
+                                          _I, _I, _I, _I, _I, _P]),
     "gtg_moe_arrange": ("experts", [_P, _I, _I, _I, _I, _P, _P, _P, _P]),
     "gtg_moe_product_simt": ("experts", [_I, _I, _P, _I, _P, _I, _P, _I, _L, _P, _I, _P, _I, _I, _I, _P]),
     "gtg_moe_combine": ("experts", [_I, _P, _I, _P, _P, _P, _I, _I, _I, _P]),
@@ -259,13 +263,13 @@ def _check_access(what: str, mode: int, kv, slots, positions=None, token_seq=Non
 
 
 # ------------------------------------------------------------------ elementwise
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[n,:] (float32) = table[tokens[n],:]."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[n,:] (float32) = table[tokens[n],:] * scale."""
     N, (V, H) = tokens.numel(), table.shape
     _need(tokens.dtype == torch.int32 and tokens.is_contiguous(), "embed: tokens must be contiguous int32")
     _need(table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32
           and tuple(out.shape) == (N, H), "embed: out must be contiguous float32 [N, H]")
-    _check(_fn("gtg_embed")(_dt(table), _ptr(tokens), _ptr(table), _ptr(out), N, H, V, _stream()), "embed")
+    _check(_fn("gtg_embed")(_dt(table), _ptr(tokens), _ptr(table), _ptr(out), N, H, V, float(scale), _stream()), "embed")
 
 
 def add_rmsnorm(residual: torch.Tensor, pending: Optional[torch.Tensor], weight: torch.Tensor,
@@ -433,6 +437,79 @@ def rmsnorm_add(update: torch.Tensor, weight: torch.Tensor, eps: float, residual
     _need(update.dtype == torch.float32 or _dt(update) == dt, "rmsnorm_add: update must be float32 or of the image's dtype")
     _check(_fn("gtg_rmsnorm_add")(dt, 1 if update.dtype == torch.float32 else 0, _ptr(update), _ptr(bias), _ptr(weight),
                                   float(eps), _ptr(residual), _ptr(image), N, H, _stream()), "rmsnorm_add")
+
+
+HYPER_MAX_COPIES = 8
+
+
+def hyper_norm(copies: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
+               seed: Optional[torch.Tensor] = None, update: Optional[torch.Tensor] = None,
+               mix: Optional[torch.Tensor] = None, out_w: Optional[torch.Tensor] = None,
+               in_w: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """The hidden state in S copies, float32 [N, S, H].  With `update` y [N, H] (float32 or
+    out's dtype) first x_t <- sum_s mix[s, t] x_s + out_w[t] y, all copies at once; then
+    out = rmsnorm(sum_t in_w[t] x_t) * weight (in_w None: the plain sum).  With `seed`
+    [N, H] the copies are made: each is the seed's row.  With `rows` only those
+    tokens are read, nothing is written back, and out has len(rows) rows."""
+    _need(copies.dtype == torch.float32 and copies.is_contiguous() and copies.dim() == 3,
+          "hyper_norm: the copies must be contiguous float32 [N, S, H]")
+    N, S, H = copies.shape
+    R = rows.numel() if rows is not None else N
+    _need(S <= HYPER_MAX_COPIES, f"hyper_norm: at most {HYPER_MAX_COPIES} copies, got {S}")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == H, "hyper_norm: weight must be float32 [H]")
+    _need(out.is_contiguous() and tuple(out.shape) == (R, H), "hyper_norm: out must be contiguous [rows, H]")
+    _need(seed is None or (seed.dtype == torch.float32 and seed.is_contiguous() and tuple(seed.shape) == (N, H) and update is None),
+          "hyper_norm: the seed must be contiguous float32 [N, H], without an update")
+    if update is not None:
+        _need(update.is_contiguous() and tuple(update.shape) == (N, H) and update.dtype in (torch.float32, out.dtype),
+              "hyper_norm: the update must be contiguous [N, H], float32 or of out's dtype")
+        _need(mix is not None and out_w is not None and mix.dtype == out_w.dtype == torch.float32 and mix.is_contiguous()
+              and out_w.is_contiguous() and tuple(mix.shape) == (S, S) and out_w.numel() == S,
+              "hyper_norm: an update needs mix float32 [S, S] and out_w float32 [S]")
+    _need(in_w is None or (in_w.dtype == torch.float32 and in_w.is_contiguous() and in_w.numel() == S), "hyper_norm: in_w must be float32 [S]")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.is_contiguous(), "hyper_norm: rows must be contiguous int32")
+    _check(_fn("gtg_hyper_norm")(_dt(out), 1 if (update is not None and update.dtype == torch.float32) else 0, _ptr(copies), _ptr(seed),
+                                 _ptr(update), _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(weight), float(eps), _ptr(out), _ptr(rows),
+                                 R, S, H, _stream()), "hyper_norm")
+
+
+def qkv_finish(sums: torch.Tensor, bias: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor], n_heads: int, kv,
+               q_out: torch.Tensor, token_seq, slots, positions, *, unit_norm: bool = False, eps: float = 0.0,
+               v_first: Optional[torch.Tensor] = None, v_keep: Optional[torch.Tensor] = None, blend: float = 0.0,
+               gate_out: Optional[torch.Tensor] = None, store: bool = True) -> None:
+    """From the float sums of a fused projection [N, q | k | v | gate]: biases added, the first
+    channels of query and key heads rotated (half-split pairs, as many as the table has),
+    optionally each head divided by its root mean square, values blended with `v_first`
+    ((1 - blend) v + blend v_first; float32 [N, n_kv * value_dim]) or kept in `v_keep`
+    unblended, gate columns turned into sigmoid factors (`gate_out` float32 [N, n_heads]);
+    queries to `q_out`, keys and values into the cache `kv` (its head_dim and value_dim)."""
+    _rows2d(sums, "qkv_finish: sums"); _rows2d(q_out, "qkv_finish: q_out")
+    N = sums.shape[0]
+    hd, vd, n_kv = kv.head_dim, kv.value_dim, kv.n_kv_heads
+    biased = n_heads * hd + n_kv * (hd + vd)
+    width = biased + (n_heads if gate_out is not None else 0)
+    _need(sums.dtype == torch.float32 and sums.shape[1] >= width, f"qkv_finish: sums must be float32 with {width} columns at least")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == biased), "qkv_finish: bias must be float32 [q | k | v]")
+    rot = 0
+    if cos_sin is not None:
+        _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[0] == N and cos_sin.shape[2] == 2,
+              "qkv_finish: the rotation table must be float32 [N, pairs, 2]")
+        rot = 2 * cos_sin.shape[1]
+        _need(rot <= hd, "qkv_finish: more rotated channels than a head has")
+    _need(q_out.dtype == kv.k.dtype and q_out.shape[0] == N and q_out.shape[1] >= n_heads * hd, "qkv_finish: q_out must be [N, n_heads * head_dim] of the cache's dtype")
+    for t, name in ((v_first, "v_first"), (v_keep, "v_keep")):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == (N, n_kv * vd)), f"qkv_finish: {name} must be float32 [N, n_kv * value_dim]")
+    _need(gate_out is None or (gate_out.dtype == torch.float32 and gate_out.is_contiguous() and tuple(gate_out.shape) == (N, n_heads)),
+          "qkv_finish: gate_out must be float32 [N, n_heads]")
+    _int32("qkv_finish", token_seq, slots, positions)
+    if store:
+        _check_access("qkv_finish", 0, kv, slots, positions, token_seq, n_items=N)
+    _check(_fn("gtg_qkv_finish")(_dt(q_out), _ptr(sums), sums.stride(0), _ptr(bias), _ptr(cos_sin), rot, 1 if unit_norm else 0, float(eps),
+                                 _ptr(v_first), _ptr(v_keep), float(blend), _ptr(q_out), q_out.stride(0), _ptr(gate_out),
+                                 _ptr(kv.k) if store else None, _ptr(kv.v) if store else None, kv.page_stride, _ptr(kv.block_table),
+                                 kv.table_stride, _ptr(token_seq), _ptr(slots), _ptr(positions), N, n_heads, n_kv, hd, vd, _stream()),
+           "qkv_finish")
 
 
 def round_rows(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -804,23 +881,38 @@ def attention_bf16_supports(head_dim: int) -> bool:
 
 
 def attention_simple(q: torch.Tensor, out: torch.Tensor, kv, token_seq, slots, positions,
-                     n_heads: int, scale: float, window: int = 0, value_dim: Optional[int] = None) -> None:
+                     n_heads: int, scale: float, window: int = 0, value_dim: Optional[int] = None,
+                     chunk: int = 0, gate: Optional[torch.Tensor] = None) -> None:
     """One warp per (token, head): the float32 path's attention, for prompts and
     decode steps alike.  `value_dim`: a value is the first so many channels of a
-    row of the value plane (default: all of them), and a head of `out` is that wide."""
+    row of the value plane (default: all of them), and a head of `out` is that wide.
+    `chunk` > 0: a token sees the keys of its own stretch of `chunk` positions only.
+    `gate`: float32 [N, n_heads], a factor on each head's output."""
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
     N = q.shape[0]
-    vd = kv.head_dim if value_dim is None else int(value_dim)
+    vrow = kv.value_dim
+    vd = vrow if value_dim is None else int(value_dim)
     _need(kv.k.dtype == q.dtype == out.dtype, "attention: q, out and the cache must share a dtype")
-    _need(kv.head_dim <= 2048 and 0 < vd <= min(kv.head_dim, 1024),
-          f"attention: head_dim {kv.head_dim} exceeds 2048 or the value width {vd} exceeds 1024 or the head")
+    _need(kv.head_dim <= 2048 and 0 < vd <= min(vrow, 1024),
+          f"attention: head_dim {kv.head_dim} exceeds 2048 or the value width {vd} exceeds 1024 or the stored row")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (N, n_heads)),
+          "attention: gate must be contiguous float32 [N, n_heads]")
     _need(q.shape[1] >= n_heads * kv.head_dim and out.shape[1] >= n_heads * vd, "attention: q or out is too narrow")
     _check_access("attention_simple", 0, kv, slots, positions, token_seq, n_items=N)
     _check(_fn("gtg_attention_simple")(_dt(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0),
                                        _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
                                        kv.table_stride, _ptr(token_seq), _ptr(slots), _ptr(positions),
-                                       N, n_heads, kv.n_kv_heads, kv.head_dim, vd, float(scale), int(window),
-                                       _stream()), "attention_simple")
+                                       N, n_heads, kv.n_kv_heads, kv.head_dim, vd, vrow, float(scale), int(window),
+                                       int(chunk), _ptr(gate), _stream()), "attention_simple")
+
+
+def attention_general(q: torch.Tensor, out: torch.Tensor, kv, ctx, n_heads: int, scale: float, window: int = 0,
+                      chunk: int = 0, gate: Optional[torch.Tensor] = None) -> None:
+    """Attention for mixers whose keys and values differ in size, whose keys are seen
+    within stretches of `chunk` positions, or whose heads carry a gate: `ctx` is the
+    step's context (rows, positions, sequences).  out[n, h] = gate[n, h] *
+    softmax(q . K * scale over the visible keys) V."""
+    attention_simple(q, out, kv, ctx.token_seq, ctx.slots, ctx.positions, n_heads, scale, window, chunk=chunk, gate=gate)
 
 
 def attention_prefill_bf16(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int, max_q_len: int,
@@ -1078,10 +1170,15 @@ def expanded_attention_bf16(q: torch.Tensor, runs: torch.Tensor, out: torch.Tens
 MOE_TILE_ROWS = 64
 
 
+MOE_SCORING = {"softmax_chosen": 0, "sigmoid": 1}
+
+
 def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], chosen: torch.Tensor,
-              weights: torch.Tensor) -> None:
+              weights: torch.Tensor, scoring: str = "softmax_chosen") -> None:
     """Router logits x . router^T + bias in float; chosen[n, :] = the `top` largest
-    (ties: the lower index), weights[n, :] = softmax over those logits alone."""
+    (ties: the lower index), weights[n, :] = softmax over those logits alone
+    ("softmax_chosen") or each chosen logit's own sigmoid ("sigmoid")."""
+    _need(scoring in MOE_SCORING, f"moe_route: scoring {scoring!r} is not known; known: {sorted(MOE_SCORING)}")
     _rows2d(x, "moe_route: x")
     N, H = x.shape
     E, top = router.shape[0], chosen.shape[1]
@@ -1091,7 +1188,7 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor
           and tuple(chosen.shape) == (N, top) and tuple(weights.shape) == (N, top) and 0 < top <= E,
           "moe_route: chosen int32 [N, top] and weights float32 [N, top]")
     _check(_fn("gtg_moe_route")(_dt(x), _ptr(x), x.stride(0), _ptr(router), _ptr(bias), _ptr(chosen), _ptr(weights), N, H, E, top,
-                                _stream()), "moe_route")
+                                MOE_SCORING[scoring], _stream()), "moe_route")
 
 
 def moe_tiles_cap(n_items: int, n_experts: int, tile: int = MOE_TILE_ROWS) -> int:
@@ -1112,10 +1209,22 @@ def moe_arrange(chosen: torch.Tensor, n_experts: int, row_item: torch.Tensor, it
                                   _stream()), "moe_arrange")
 
 
-def moe_gather(x: torch.Tensor, row_item: torch.Tensor, item_div: int, out: torch.Tensor) -> None:
+def moe_gather(x: torch.Tensor, row_item: torch.Tensor, item_div: int, out: torch.Tensor,
+               weights: Optional[torch.Tensor] = None) -> None:
     """out[row, :] = x[row_item[row] // item_div, :], zeros for padding rows: the inputs of a
-    step's (token, expert) pairs in arranged order (bfloat16, a multiple of 8 channels)."""
+    step's (token, expert) pairs in arranged order (bfloat16, a multiple of 8 channels).
+    With `weights` (float32, one per pair) a row is weights[pair] * x[token, :], the product
+    in float and rounded once; that form takes either dtype and any width."""
     _rows2d(x, "moe_gather: x")
+    if weights is not None or x.dtype != torch.bfloat16 or x.shape[1] % 8 or x.stride(0) % 8:
+        _need(out.dtype == x.dtype and out.is_contiguous() and tuple(out.shape) == (row_item.numel(), x.shape[1]),
+              "moe_gather: out must be contiguous [rows, H] of x's dtype")
+        _need(weights is None or (weights.dtype == torch.float32 and weights.is_contiguous()),
+              "moe_gather: weights must be contiguous float32, one per pair")
+        _int32("moe_gather", row_item)
+        _check(_fn("gtg_moe_gather_scaled")(_dt(x), _ptr(x), x.stride(0), _ptr(row_item), int(item_div), _ptr(weights), _ptr(out),
+                                            out.shape[0], x.shape[1], _stream()), "moe_gather")
+        return
     _need(x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.is_contiguous()
           and tuple(out.shape) == (row_item.numel(), x.shape[1]), "moe_gather: bfloat16 x [N, H] and out [rows, H]")
     _int32("moe_gather", row_item)
@@ -1142,7 +1251,12 @@ def moe_product(a: torch.Tensor, row_item: torch.Tensor, item_div: int, w: torch
     E, N, K = w.shape
     cap = tile_expert.numel()
     tile = out.shape[0] // max(cap, 1)
-    _need(epilogue in ("none", "swiglu"), f"moe_product: unknown epilogue {epilogue!r}")
+    _need(epilogue in ("none", "swiglu") or epilogue in ACTIVATIONS, f"moe_product: unknown epilogue {epilogue!r}")
+    if epilogue in ACTIVATIONS:
+        # an activation of the product: on the float sums where the kernel has the epilogue, else behind it
+        moe_product(a, row_item, item_div, w, tile_expert, out)
+        activation(out, epilogue)
+        return
     n_out = N // 2 if epilogue == "swiglu" else N
     _need(w.is_contiguous() and a.dtype == w.dtype and a.shape[1] == K, "moe_product: a [*, K] and contiguous w [E, N, K] of one dtype")
     _need(tuple(out.shape) == (cap * tile, n_out) and out.dtype in (a.dtype, torch.float32), "moe_product: out must be [tiles * tile, N]")
@@ -1170,14 +1284,15 @@ def moe_product(a: torch.Tensor, row_item: torch.Tensor, item_div: int, w: torch
                                        _stream()), "moe_product")
 
 
-def moe_combine(y: torch.Tensor, item_row: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
+def moe_combine(y: torch.Tensor, item_row: torch.Tensor, weights: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """out[t, :] = sum_k weights[t, k] * y[item_row[t * top + k], :] (float sums, k in
-    order; out float32 or bfloat16)."""
+    order; out float32 or bfloat16).  weights None: the plain sum of a token's rows."""
     _rows2d(y, "moe_combine: y")
-    N, top = weights.shape
+    N = out.shape[0]
+    top = item_row.numel() // max(N, 1)
     H = y.shape[1]
-    _need(y.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (N, H)
-          and weights.dtype == torch.float32 and weights.is_contiguous() and item_row.numel() == N * top,
+    _need(y.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (N, H) and item_row.numel() == N * top
+          and (weights is None or (weights.dtype == torch.float32 and weights.is_contiguous() and tuple(weights.shape) == (N, top))),
           "moe_combine: y float32 [rows, H], weights float32 [N, top], out [N, H]")
     _int32("moe_combine", item_row)
     _check(_fn("gtg_moe_combine")(_dt(out), _ptr(y), y.stride(0), _ptr(item_row), _ptr(weights), _ptr(out), N, H, top, _stream()),

@@ -15,6 +15,26 @@ its key as projected, before the rotation), and the tensor names ``q``, ``k``,
 ``v``, ``o``.  The projections are fused at load into one matrix
 [(n_heads + 2 n_kv_heads) * head_dim, hidden] (without the value rows when the
 values are the keys) so that one product serves them.
+
+Further options, none of which the reference has; a mixer that uses any of them
+takes the general route (`_forward_general`): the fused projection leaves float
+sums, one kernel finishes them (`ops.qkv_finish`: biases, rotation, unit norm,
+value blend, gate, cache store, all in float and rounded once), and the
+attention kernels that know the options follow.
+``value_dim``: channels of a value head where they differ from a key head's
+(the cache then keeps value rows of that width, the output projection reads
+n_heads * value_dim columns).  ``q_bias``, ``k_bias``, ``v_bias``: tensor names
+of biases added in the projection (all three or none).  ``qk_norm`` "unit":
+after the rotation every query and key head is divided by its root mean square
+over the head, x / sqrt(mean(x^2) + ``norm_eps``), without a weight.  ``chunk``:
+positions are cut into stretches of so many, counted from the sequence's first
+token, and a query sees the keys at or before it within its own stretch only.
+``head_gate``: tensor name [n_heads, hidden]; head h's output is multiplied by
+sigmoid(gate_h . x) before the output projection.  ``value_blend``: {"role":
+"source" | "blend", "weight": tensor name of a scalar, "key": a name}: the
+"source" layer leaves its values for the step under the key, a "blend" layer
+caches and attends (1 - w) v + w v_source for the same token (the source's own
+scalar exists in the checkpoint and is not read).
 """
 from __future__ import annotations
 
@@ -53,6 +73,31 @@ class GQAttention(Mixer):
         self.names = {k: str(self.param(k)) for k in wanted}
         self.q_dim = self.n_heads * self.head_dim
         self.kv_dim = self.n_kv * self.head_dim
+        # ---- options of the general route
+        self.value_dim = int(self.p.get("value_dim") or self.head_dim)
+        self.v_width = self.n_kv * self.value_dim
+        biases = [self.p.get(k) for k in ("q_bias", "k_bias", "v_bias")]
+        if any(biases) and not all(biases):
+            raise ValueError("an attention mixer has biases on q, k and v or on none of them")
+        self.bias_names = [str(b) for b in biases] if all(biases) else None
+        self.qk_norm = self.p.get("qk_norm")
+        if self.qk_norm not in (None, "unit"):
+            raise ValueError(f"qk_norm {self.qk_norm!r} is not known: None or 'unit'")
+        self.norm_eps = float(self.p.get("norm_eps") or 0.0)
+        chunk = self.p.get("chunk")
+        self.chunk = int(chunk) if chunk else None
+        gate = self.p.get("head_gate")
+        self.gate_name = str(gate) if gate else None
+        blend = self.p.get("value_blend")
+        self.blend = dict(blend) if blend else None
+        if self.blend and self.blend.get("role") not in ("source", "blend"):
+            raise ValueError(f"value_blend role {self.blend.get('role')!r} is not known: 'source' or 'blend'")
+        self.general = bool(self.value_dim != self.head_dim or self.bias_names or self.qk_norm or self.chunk
+                            or self.gate_name or self.blend)
+        if self.general and (self.v_from_k or not self.own_kv):
+            raise ValueError("the options of the general attention route need key and value projections of the layer's own")
+        self.bias: Optional[torch.Tensor] = None
+        self.blend_weight = 0.0
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
 
@@ -61,15 +106,28 @@ class GQAttention(Mixer):
         if self.own_kv:
             specs.append(WeightSpec(self.names["k"], (self.kv_dim, self.hidden)))
             if not self.v_from_k:
-                specs.append(WeightSpec(self.names["v"], (self.kv_dim, self.hidden)))
-        specs.append(WeightSpec(self.names["o"], (self.hidden, self.q_dim)))
+                specs.append(WeightSpec(self.names["v"], (self.v_width, self.hidden)))
+        specs.append(WeightSpec(self.names["o"], (self.hidden, self.n_heads * self.value_dim)))
+        if self.bias_names:
+            specs += [WeightSpec(name, (size,), role="parameter", std=0.02)
+                      for name, size in zip(self.bias_names, (self.q_dim, self.kv_dim, self.v_width))]
+        if self.gate_name:
+            specs.append(WeightSpec(self.gate_name, (self.n_heads, self.hidden)))
+        if self.blend:
+            source = self.blend["role"] == "source"
+            specs.append(WeightSpec(str(self.blend["weight"]), (), role="ignored" if source else "parameter",
+                                    optional=source, mean=0.3, std=0.1))
         return specs
 
     def children(self):
         return [self.position]
 
     def cache_requests(self) -> List[Request]:
-        return [KVRequest(self.n_kv, self.head_dim, self.window)] if self.own_kv else []
+        if not self.own_kv:
+            return []
+        if self.general:
+            return [KVRequest(self.n_kv, self.head_dim, self.window, value_dim=self.value_dim, chunk=self.chunk)]
+        return [KVRequest(self.n_kv, self.head_dim, self.window)]
 
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         parts = [tensors[self.names["q"]]]
@@ -77,14 +135,61 @@ class GQAttention(Mixer):
             parts.append(tensors[self.names["k"]])
             if not self.v_from_k:
                 parts.append(tensors[self.names["v"]])
+        if self.gate_name:
+            parts.append(tensors[self.gate_name])
+        rows = sum(p.shape[0] for p in parts)
+        if self.general and rows % 8:
+            # whole groups of 8 rows, so that the products' float sums keep rows of a multiple of 32 bytes
+            parts.append(torch.zeros((8 - rows % 8, self.hidden), dtype=parts[0].dtype))
         self.w_qkv = rt.matrix(torch.cat([p.to(rt.dtype) for p in parts], dim=0))
         self.w_o = rt.matrix(tensors[self.names["o"]])
+        if self.bias_names:
+            self.bias = rt.vector(torch.cat([tensors[name].reshape(-1).to(torch.float32) for name in self.bias_names]))
+        if self.blend and self.blend["role"] == "blend":
+            self.blend_weight = float(tensors[str(self.blend["weight"])].to(torch.float32))
+
+    def _forward_general(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
+        rt = ctx.rt
+        kv = cache.kv
+        n = x.shape[0]
+        sums = rt.empty(n, self.w_qkv.shape[0], dtype=torch.float32)
+        ops.linear(x, self.w_qkv, sums)
+        rotation = self.position.rotation(ctx)
+        if rotation is not None and self.position.pairing != "half":
+            raise ValueError("the general attention route rotates half-split pairs only")
+        q = rt.empty(n, self.q_dim)
+        gate = rt.empty(n, self.n_heads, dtype=torch.float32) if self.gate_name else None
+        v_first = v_keep = None
+        if self.blend:
+            key = ("value_blend", self.blend.get("key"))
+            if self.blend["role"] == "source":
+                v_keep = rt.empty(n, self.v_width, dtype=torch.float32, lifetime="step")
+                ctx.shared[key] = v_keep
+            else:
+                v_first = ctx.shared.get(key)
+                if v_first is None or tuple(v_first.shape) != (n, self.v_width):
+                    raise ValueError("no layer of this step has left values of this layer's shape to blend with")
+        ops.qkv_finish(sums, self.bias, rotation, self.n_heads, kv, q, ctx.token_seq, ctx.slots, ctx.positions,
+                       unit_norm=self.qk_norm == "unit", eps=self.norm_eps, v_first=v_first, v_keep=v_keep,
+                       blend=self.blend_weight, gate_out=gate, store=cache.writes)
+        ctx.trace("q_attn", q)
+        mixed = rt.empty(n, self.n_heads * self.value_dim)
+        ops.attention_general(q, mixed, kv, ctx, self.n_heads, self.scale, window=self.window or 0,
+                              chunk=self.chunk or 0, gate=gate)
+        ctx.trace("attn", mixed)
+        if ctx.float_updates:
+            out = rt.empty(n, self.hidden, dtype=torch.float32)
+            ops.linear(mixed, self.w_o, out)
+            return out
+        return emit_update(mixed, self.w_o, ctx)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
         rt = ctx.rt
         kv = cache.kv
-        if kv is None or kv.n_kv_heads != self.n_kv or kv.head_dim != self.head_dim:
+        if kv is None or kv.n_kv_heads != self.n_kv or kv.head_dim != self.head_dim or kv.value_dim != self.value_dim:
             raise ValueError("attention was given a cache entry that does not match its heads")
+        if self.general:
+            return self._forward_general(x, ctx, cache)
         n = x.shape[0]
         qkv = rt.empty(n, self.w_qkv.shape[0])
         rotation = self.position.rotation(ctx)

@@ -271,12 +271,22 @@ class ResidualStream:
     adds the pending update and normalises in one pass.  `image` is the residual
     rounded to the compute dtype, or None: whoever changes the residual either
     writes the image along with it or sets it None; a part that reads the hidden
-    state itself (not a norm of it) reads the image and makes it when it is None."""
+    state itself (not a norm of it) reads the image and makes it when it is None.
+
+    A block that keeps the hidden state in several copies (hyper-connections)
+    sets `copies`, float32 [N, S, H]; from then on the hidden state is their sum
+    and `residual` is no longer current.  A pending update then joins every copy
+    with a weight of its own while the copies are remixed: `pending_links` holds
+    (mix [S, S] indexed [from, to], out [S]) for it, x_t <- sum_s mix[s, t] x_s +
+    out[t] pending.  A norm that is handed such a stream applies the update and
+    norms the copies' sum (`ops.hyper_norm`)."""
 
     def __init__(self, residual: torch.Tensor, pending: Optional[torch.Tensor] = None):
         self.residual = residual
         self.pending = pending
         self.image: Optional[torch.Tensor] = None
+        self.copies: Optional[torch.Tensor] = None
+        self.pending_links = None
 
 
 def emit_update(x: torch.Tensor, w: torch.Tensor, ctx: "StepContext") -> Optional[torch.Tensor]:

@@ -1,8 +1,9 @@
 """Token embedding and the output head.
 
-``token_embedding``: x = E[token], unscaled (model/inference_helpers.go:9-34);
+``token_embedding``: x = E[token] (unscaled: model/inference_helpers.go:9-34),
+or E[token] * ``scale`` where a scale is given;
 it starts the float32 residual stream.  Parameters: ``vocab_size``,
-``hidden_size``, ``weight`` and optionally ``position`` (a position PartSpec
+``hidden_size``, ``weight`` and optionally ``scale``, ``position`` (a position PartSpec
 whose `on_embedding` hook acts on the embedded tokens) and ``keep_output``
 (True: a float32 copy of the embedded tokens stays in the step's shared values
 as "embedding_output" for later parts to read).
@@ -36,6 +37,7 @@ class TokenEmbedding(Embedding):
         pos = self.p.get("position")
         self.position = build_part("position", pos) if pos is not None else None
         self.keep_output = bool(self.p.get("keep_output", False))
+        self.scale = float(self.p.get("scale") or 1.0)
         self.table: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -49,10 +51,10 @@ class TokenEmbedding(Embedding):
 
     def forward(self, ctx: StepContext) -> ResidualStream:
         residual = ctx.rt.empty(ctx.n_tokens, self.hidden, dtype=torch.float32, lifetime="step")
-        ops.embed(ctx.tokens, self.table, residual)
+        ops.embed(ctx.tokens, self.table, residual, self.scale)
         if self.keep_output:
             kept = ctx.rt.empty(ctx.n_tokens, self.hidden, dtype=torch.float32, lifetime="step")
-            ops.embed(ctx.tokens, self.table, kept)
+            ops.embed(ctx.tokens, self.table, kept, self.scale)
             ctx.shared["embedding_output"] = kept
         stream = ResidualStream(residual)
         if self.position:

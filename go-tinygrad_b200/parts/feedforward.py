@@ -32,7 +32,13 @@ rows up in float, always in the order of its choices: no result depends on the
 batch, and nothing talks to the host.  Parameters: ``hidden_size``,
 ``intermediate_size``, ``n_experts``, ``top``, the tensor names ``router``,
 ``router_bias`` (None: no bias) and ``gate``, ``up``, ``down`` with ``{e}``
-standing for the expert's index.  The reference has no routed feed-forward.
+standing for the expert's index.  Options: ``gate`` None makes the experts
+ungated, down(act(up(x))) with ``activation`` ("relu2", "gelu_tanh", "silu");
+``scoring`` "sigmoid" makes a chosen expert's weight the sigmoid of its own
+logit, not renormalised (the largest sigmoids are the largest logits);
+``weight_on`` "input" multiplies the expert's input by the weight instead of
+its output: the update is the plain sum of expert(weight * x), the scaled rows
+formed in float and rounded once.  The reference has no routed feed-forward.
 """
 from __future__ import annotations
 
@@ -130,8 +136,21 @@ class RoutedExperts(FeedForward):
         self.top = int(self.param("top"))
         if not 0 < self.top <= self.n_experts:
             raise ValueError(f"a token cannot use {self.top} of {self.n_experts} experts")
-        self.names = {k: str(self.param(k)) for k in ("router", "gate", "up", "down")}
-        for k in ("gate", "up", "down"):
+        self.gated = self.p.get("gate") is not None
+        self.activation = str(self.p.get("activation") or ("silu" if self.gated else "relu2"))
+        if self.gated and self.activation != "silu":
+            raise ValueError("gated experts use the silu activation")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"expert activation {self.activation!r} is not known; known: {sorted(ops.ACTIVATIONS)}")
+        self.scoring = str(self.p.get("scoring") or "softmax_chosen")
+        if self.scoring not in ops.MOE_SCORING:
+            raise ValueError(f"router scoring {self.scoring!r} is not known; known: {sorted(ops.MOE_SCORING)}")
+        self.weight_on = str(self.p.get("weight_on") or "output")
+        if self.weight_on not in ("input", "output"):
+            raise ValueError(f"an expert's weight multiplies its 'input' or its 'output', not {self.weight_on!r}")
+        self.matrices = ("gate", "up", "down") if self.gated else ("up", "down")
+        self.names = {k: str(self.param(k)) for k in ("router",) + self.matrices}
+        for k in self.matrices:
             if "{e}" not in self.names[k]:
                 raise ValueError(f"the experts' tensor name {self.names[k]!r} needs '{{e}}' for the expert's index")
         bias = self.p.get("router_bias")
@@ -146,8 +165,9 @@ class RoutedExperts(FeedForward):
         if self.router_bias_name:
             specs.append(WeightSpec(self.router_bias_name, (self.n_experts,), role="parameter", std=0.02))
         for e in range(self.n_experts):
-            specs += [WeightSpec(self._name("gate", e), (self.inter, self.hidden)),
-                      WeightSpec(self._name("up", e), (self.inter, self.hidden)),
+            if self.gated:
+                specs.append(WeightSpec(self._name("gate", e), (self.inter, self.hidden)))
+            specs += [WeightSpec(self._name("up", e), (self.inter, self.hidden)),
                       WeightSpec(self._name("down", e), (self.hidden, self.inter))]
         return specs
 
@@ -157,6 +177,10 @@ class RoutedExperts(FeedForward):
         # [E, 2I, H]: an expert's gate rows, then its up rows -- or, where the products run on the
         # tensor cores and apply the gated silu in their epilogue, alternating in blocks of 8; [E, H, I]
         self.fused = rt.dtype == torch.bfloat16 and self.inter % 8 == 0 and self.hidden % 8 == 0
+        if not self.gated:
+            self.w_gate_up = rt.matrix(torch.stack([tensors[self._name("up", e)].to(rt.dtype) for e in range(self.n_experts)]))
+            self.w_down = rt.matrix(torch.stack([tensors[self._name("down", e)].to(rt.dtype) for e in range(self.n_experts)]))
+            return
         both = (lambda g, u: ops.interleave_gate_up(g, u)) if self.fused else (lambda g, u: torch.cat([g, u], dim=0))
         self.w_gate_up = rt.matrix(torch.stack([both(tensors[self._name("gate", e)].to(rt.dtype),
                                                      tensors[self._name("up", e)].to(rt.dtype))
@@ -168,8 +192,10 @@ class RoutedExperts(FeedForward):
         n, top, E = x.shape[0], self.top, self.n_experts
         chosen = rt.empty(n, top, dtype=torch.int32)
         weights = rt.empty(n, top, dtype=torch.float32)
-        ops.moe_route(x, self.router, self.router_bias, chosen, weights)
+        ops.moe_route(x, self.router, self.router_bias, chosen, weights, self.scoring)
         ctx.trace("experts", chosen)
+        if not self.gated or self.weight_on == "input":
+            return self._forward_general(x, ctx, chosen, weights)
         fused = self.fused and ops.moe_product_fused_supports(x, self.w_gate_up)
         # tiles of 128 rows once the experts have that many tokens each on average
         tile = 128 if fused and n * top >= 128 * E else ops.MOE_TILE_ROWS
@@ -195,6 +221,40 @@ class RoutedExperts(FeedForward):
         ops.moe_product(act, row_item, 0, self.w_down, tile_expert, y)
         out = rt.empty(n, self.hidden, dtype=torch.float32 if ctx.float_updates else None)
         ops.moe_combine(y, item_row, weights, out)
+        return out
+
+
+    def _forward_general(self, x: torch.Tensor, ctx: StepContext, chosen: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """Ungated experts and weights on the input: the step's (token, expert) rows are
+        copied into arranged order (times their weights where those scale the input),
+        and both products run over arranged rows."""
+        rt = ctx.rt
+        n, top, E = x.shape[0], self.top, self.n_experts
+        fused = self.fused and ops.moe_product_fused_supports(x, self.w_gate_up)
+        tile = 128 if fused and n * top >= 128 * E else ops.MOE_TILE_ROWS
+        tiles = ops.moe_tiles_cap(n * top, E, tile)
+        rows = tiles * tile
+        row_item = rt.empty(rows, dtype=torch.int32)
+        item_row = rt.empty(n * top, dtype=torch.int32)
+        tile_expert = rt.empty(tiles, dtype=torch.int32)
+        ops.moe_arrange(chosen, E, row_item, item_row, tile_expert, tile)
+        on_input = self.weight_on == "input"
+        gathered = rt.empty(rows, self.hidden)
+        ops.moe_gather(x, row_item, top, gathered, weights=weights if on_input else None)
+        act = rt.empty(rows, self.inter)
+        if self.gated and fused:
+            ops.moe_product(gathered, row_item, 0, self.w_gate_up, tile_expert, act, epilogue="swiglu")
+        elif self.gated:
+            sums = rt.empty(rows, 2 * self.inter, dtype=torch.float32)
+            ops.moe_product(gathered, row_item, 0, self.w_gate_up, tile_expert, sums)
+            ops.swiglu_bias(sums, None, None, act)
+        else:
+            ops.moe_product(gathered, row_item, 0, self.w_gate_up, tile_expert, act, epilogue=self.activation)
+        ctx.trace("gate_act", act)
+        y = rt.empty(rows, self.hidden, dtype=torch.float32)
+        ops.moe_product(act, row_item, 0, self.w_down, tile_expert, y)
+        out = rt.empty(n, self.hidden, dtype=torch.float32 if ctx.float_updates else None)
+        ops.moe_combine(y, item_row, None if on_input else weights, out)
         return out
 
 

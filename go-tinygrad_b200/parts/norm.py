@@ -4,6 +4,10 @@
 the scale in float32 (backends/simd/vec.go:72-85).  Parameters: ``size``,
 ``eps``, ``weight`` (tensor name).
 
+Handed a stream whose hidden state is kept in several copies
+(`ResidualStream.copies`), ``rmsnorm`` norms their sum and applies a pending
+update by its links on the way.
+
 ``layernorm``: y = (x - mean(x)) / sqrt(var(x) + eps) * w + b, var the mean of
 the squared deviations, all in float32.  Parameters: ``size``, ``eps``,
 ``weight`` and ``bias`` (tensor names; ``bias`` None for a norm without one).
@@ -39,6 +43,13 @@ class RMSNorm(Norm):
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n_out = rows.numel() if rows is not None else stream.residual.shape[0]
         out = ctx.rt.empty(n_out, self.size)
+        if stream.copies is not None:
+            # the hidden state is the sum of its copies; a pending update joins them by its links first
+            mix, out_w = stream.pending_links if stream.pending is not None else (None, None)
+            ops.hyper_norm(stream.copies, self.weight, self.eps, out, update=stream.pending, mix=mix, out_w=out_w, rows=rows)
+            if rows is None:
+                stream.pending, stream.pending_links, stream.image = None, None, None
+            return out
         ops.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out, rows)
         if rows is None:
             if stream.pending is not None:
