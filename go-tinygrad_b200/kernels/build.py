@@ -45,6 +45,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_bf16_grouped": "gemm_bf16_grouped.cu",
     "hyper": "hyper.cu",
     "attention_prep": "attention_prep.cu",
+    "attention_masked": "attention_masked.cu",
 }
 # sources a library's file includes textually (they count for staleness)
 INCLUDED_SOURCES: Dict[str, List[str]] = {"attention_decode_static.cu": ["attention_bf16.cu"]}

@@ -78,6 +78,11 @@ _SIGNATURES = {
     "gtg_gemm_bf16_tcgen05_grouped": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
     "gtg_moe_route": ("experts", [_I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_moe_gather_scaled": ("experts", [_I, _P, _I, _P, _I, _P, _P, _I, _I, _P]),
+    "gtg_attention_masked_supports": ("attention_masked", [_I, _I]),
+    "gtg_attention_masked_scratch_floats": ("attention_masked", [_I, _I, _I, _I]),
+    "gtg_attention_masked_splits": ("attention_masked", [_I, _I, _I, _I, _I, _I, _I]),
+    "gtg_attention_masked_bf16": ("attention_masked", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                                                       _F, _I, _I, _P, _I, _P, _P]),
     "gtg_hyper_norm": ("hyper", [_I, _I, _P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P]),
     "gtg_qkv_finish": ("attention_prep", [_I, _P, _I, _P, _P, _I, _I, _F, _P, _P, _F, _P, _I, _P, _P, _P, _L, _P, _I, _P, _P, _P,
                                           _I, _I, _I, _I, _I, _P]),
@@ -101,6 +106,7 @@ _SIGNATURES = {
     "gtg_sample_temperature": ("sampling", [_P, _I, _I, _I, _F, _U, _P, _P, _P, _P]),
 }
 _RESTYPES = {"gtg_attention_decode_scratch_floats": c_longlong,
+             "gtg_attention_masked_scratch_floats": c_longlong,
              "gtg_gemm_bf16_swapab_scratch_floats": c_longlong}
 
 _FUNCS = {}
@@ -911,8 +917,52 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kv, ctx, n_heads: int,
     """Attention for mixers whose keys and values differ in size, whose keys are seen
     within stretches of `chunk` positions, or whose heads carry a gate: `ctx` is the
     step's context (rows, positions, sequences).  out[n, h] = gate[n, h] *
-    softmax(q . K * scale over the visible keys) V."""
+    softmax(q . K * scale over the visible keys) V.  bfloat16 heads of a multiple of 8
+    channels up to 128 take the tensor-core kernel (`attention_masked_bf16`); float32
+    and other widths the plain one."""
+    if q.dtype == torch.bfloat16 and attention_masked_supports(kv) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and scale > 0:
+        splits = int(_fn("gtg_attention_masked_splits")(ctx.n_seqs, ctx.max_q_len, n_heads, kv.n_kv_heads, ctx.max_kv_len,
+                                                        int(window), int(chunk)))
+        scratch = None
+        if splits > 1:
+            scratch = ctx.rt.empty(int(_fn("gtg_attention_masked_scratch_floats")(q.shape[0], n_heads, kv.value_dim, splits)),
+                                   dtype=torch.float32)
+        attention_masked_bf16(q, out, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, ctx.n_seqs, ctx.max_q_len, n_heads, scale,
+                              window, chunk, gate, splits, scratch)
+        return
     attention_simple(q, out, kv, ctx.token_seq, ctx.slots, ctx.positions, n_heads, scale, window, chunk=chunk, gate=gate)
+
+
+def attention_masked_supports(kv) -> bool:
+    return (kv.k.dtype == torch.bfloat16 and bool(_fn("gtg_attention_masked_supports")(kv.head_dim, kv.value_dim))
+            and kv.page_stride % 8 == 0)
+
+
+def attention_masked_bf16(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int, max_q_len: int, n_heads: int, scale: float,
+                          window: int = 0, chunk: int = 0, gate: Optional[torch.Tensor] = None, n_splits: int = 1,
+                          scratch: Optional[torch.Tensor] = None) -> None:
+    """The tensor-core form of `attention_general`: rows are (token, query head of a group)
+    pairs, a block of 64 rows reads each page once for the group.  Prompts, portions and
+    decode steps alike; `n_splits` > 1 cuts every tile's pages into that many shares, merged
+    through `scratch` (float32, `gtg_attention_masked_scratch_floats`)."""
+    _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
+    N = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16, "attention_masked_bf16: bfloat16 only")
+    _need(q.shape[1] >= n_heads * kv.head_dim and out.shape[1] >= n_heads * kv.value_dim, "attention: q or out is too narrow")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (N, n_heads)),
+          "attention: gate must be contiguous float32 [N, n_heads]")
+    _need(scale > 0, "attention_masked_bf16: the scale must be positive")
+    _int32("attention", cu_seqlens, slots, start_pos)
+    if n_splits > 1:
+        need = int(_fn("gtg_attention_masked_scratch_floats")(N, n_heads, kv.value_dim, n_splits))
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
+              f"attention_masked_bf16: {n_splits} shares need {need} floats of scratch")
+    _check_access("attention_masked_bf16", 2, kv, slots, start_pos=start_pos, cu_seqlens=cu_seqlens)
+    _check(_fn("gtg_attention_masked_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), _ptr(kv.v), kv.page_stride,
+                                            _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens), _ptr(slots), _ptr(start_pos),
+                                            int(n_seqs), int(max_q_len), N, n_heads, kv.n_kv_heads, kv.head_dim, kv.value_dim,
+                                            float(scale), int(window), int(chunk), _ptr(gate), int(n_splits), _ptr(scratch), _stream()),
+           "attention_masked_bf16")
 
 
 def attention_prefill_bf16(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int, max_q_len: int,

@@ -168,7 +168,7 @@ def forward(cfg, W, tokens, experts_of=None, layers_out=None):
     eps = cfg["norm"]["eps"]
     m = float(cfg.get("residual_mult", 1.0))
     S = cfg.get("streams")
-    x0 = np.asarray(W["embed"], F64)[np.asarray(tokens)] * cfg["embedding"]["scale"]
+    x0 = np.asarray(W["embed"], F64)[np.asarray(tokens)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     xs = np.stack([x0] * (S or 1))
     v_first = None
 
@@ -208,3 +208,11 @@ def forward(cfg, W, tokens, experts_of=None, layers_out=None):
             layers_out.append(xs.sum(axis=0))
     x = xs.sum(axis=0)
     return rms_norm(x, W["final.norm"], eps) @ np.asarray(W["embed"], F64).T
+
+
+def greedy(cfg, W, prompt, n_new):
+    """n_new tokens, each the first maximum of the logits after everything before it."""
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(np.argmax(forward(cfg, W, seq)[-1])))
+    return seq[len(prompt):]
