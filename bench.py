@@ -33,7 +33,10 @@ layer sizes of two real models, beside the Llama decoder at equal width, depth
 and heads, and every kernel the design added beside the like kernel of the
 Llama path, each against the copy peak.  With --design senupel it does the same
 for the Senupel design (attention through a latent, dense and routed
-feed-forwards; see `senupel_shape`).  The default run is not changed by either.
+feed-forwards; see `senupel_shape`), and with --design zotolix for the Zotolix
+design (four copies of the hidden state, attention within stretches of
+positions, squared-relu experts; see `zotolix_shape`).  The default run is not
+changed by any of them.
 
 Peaks come from MEASURED_PEAKS.json beside this file if present, else from the
 fallback figures of an earlier measurement on the same pool.  Inputs are larger
@@ -487,6 +490,20 @@ def senupel_shape(width, heads, ff, experts, expert_ff, top, window=4096, vocab=
             "layers": [{"type": "latent_attention", "mixer": mixer(i), "mlp": routed if i % 2 else dense} for i in range(8)]}
 
 
+def zotolix_shape(width, heads, kv_heads, dim, experts, expert_ff, top, vocab=32000):
+    """Eight layers, unit-norm attention and gated attention in turn, keys seen within
+    stretches of 1,024 positions in the even layers and of 8,192 in the odd ones, half of a head
+    rotating, every layer's values blended with the first layer's; each token goes to `top` of
+    `experts` squared-relu experts; four copies of the hidden state."""
+    def mixer(i):
+        return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "v_mix": True,
+                "mask": {"size": 8192 if i % 2 else 1024}, "rot": {"dims": dim // 2, "base": 500000.0}}
+    routed = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    return {"architecture": "Zotolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 8.0},
+            "residual_mult": 0.5, "streams": 4,
+            "layers": [{"type": "attention_2" if i % 2 else "attention", "mixer": mixer(i), "mlp": routed} for i in range(8)]}
+
+
 DESIGN_SIZES = {
     # the layer sizes of Llama-3.2-1B / SmolLM2 (width 2048) and of Llama-3.1-8B (width 4096); the
     # recurrence has twice the width in its inner size, heads of 64 and a state of 128, as Mamba-2 models do
@@ -500,7 +517,17 @@ SENUPEL_SIZES = {
     "w2048": (senupel_shape(2048, 16, 8192, 16, 2048, 4), dict(LLAMA_3P2_1B, num_hidden_layers=8, vocab_size=32000)),
     "w4096": (senupel_shape(4096, 32, 14336, 16, 3584, 4), dict(LLAMA_3P1_8B, num_hidden_layers=8, vocab_size=32000)),
 }
+ZOTOLIX_SIZES = {
+    # the same two widths and heads as the Llama layers beside them; 16 experts of a quarter of the dense
+    # feed-forward's size, four to a token: as many multiplications a token as the dense feed-forward's up and down
+    "w2048": (zotolix_shape(2048, 32, 8, 64, 16, 2048, 4), dict(LLAMA_3P2_1B, num_hidden_layers=8, vocab_size=32000)),
+    "w4096": (zotolix_shape(4096, 32, 8, 128, 16, 3584, 4), dict(LLAMA_3P1_8B, num_hidden_layers=8, vocab_size=32000)),
+}
 DESIGNS = {
+    "zotolix": (ZOTOLIX_SIZES, "8 layers of attention within stretches of 1024 and 8192 positions (unit-norm and gated in turn, biased "
+                               "projections, values blended with the first layer's), mixtures of 16 squared-relu experts (4 to a token, "
+                               "the router's sigmoid on the input), four copies of the hidden state, beside 8 Llama layers of equal "
+                               "width, heads and feed-forward size; vocabulary 32000"),
     "ropovik": (DESIGN_SIZES, "4 layers (mamba2, attention, mamba2, attention, a dense feed-forward each) run twice, "
                               "beside 8 Llama layers of equal width, heads and feed-forward size; vocabulary 32000"),
     "senupel": (SENUPEL_SIZES, "8 layers of attention through a latent (a window of 4096), dense gated feed-forwards with biases "
@@ -711,6 +738,116 @@ def run_design(args):
             del cache
         return rows
 
+    def zotolix_kernel_table(cfg):
+        """Each kernel the Zotolix design added or extended, alone, at this size: a prompt of T
+        tokens and a decode step of 64 sequences after 1,024 tokens; the bytes it has to move
+        against the copy peak and, for products and attention, its FLOPs against the matrix
+        peak.  Beside each the like kernel of the Llama path (of the Senupel path for the
+        experts) at the same rows."""
+        from go_tinygrad_b200.cache import Cache, KVRequest
+        from go_tinygrad_b200.parts.base import StepContext
+        bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+        m, ex = cfg["layers"][0]["mixer"], cfg["layers"][0]["mlp"]
+        H, heads, n_kv, hd, vd, chunk, S = cfg["width"], m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"], cfg["streams"]
+        E, eff, top = ex["router"]["experts"], ex["expert"]["ff"], ex["router"]["top"]
+        rows = []
+
+        def add(name, rows_n, ms, nbytes, flops=0, like=None):
+            rows.append({"kernel": name, "rows": rows_n, "us": round(ms * 1e3, 2), "mb": round(nbytes / 1e6, 2),
+                         "of_copy_peak": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3),
+                         **({"tflops": round(flops / ms / 1e9, 1), "of_matrix_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)} if flops else {}),
+                         **({"like": like} if like else {})})
+        rnd = lambda *shape, dtype=bf: torch.randn(*shape, device=dev, dtype=f32).to(dtype)
+        for n, n_seqs, ctx_len, tag in ((T, 1, 0, "prompt"), (64, 64, prompt_len, "decode")):
+            per = n // n_seqs
+            rt = lib.parts.Runtime(dev, bf)
+            cache = Cache([[KVRequest(n_kv, hd, None, value_dim=vd, chunk=chunk)], [KVRequest(n_kv, hd, None)],
+                           [KVRequest(n_kv, hd, None, value_dim=hd // 2, chunk=chunk)]], [None, None, None],
+                          max_tokens=64 * ((ctx_len + per + 63) // 64) * n_seqs, max_slots=n_seqs, dtype=bf, device=dev)
+            slot_list = [cache.open_sequence() for _ in range(n_seqs)]
+            cache.reserve_many([(s, ctx_len + per) for s in slot_list]); cache.flush_tables()
+            for g in cache.groups:
+                g.storage.normal_()
+            kv, kv_like, kv_narrow = (h.kv for h in cache.handles)
+            cu = torch.arange(0, n + 1, per, dtype=i32, device=dev)
+            seq = torch.arange(n, dtype=i32, device=dev) // per
+            slots = torch.tensor(slot_list, dtype=i32, device=dev)
+            start = torch.full((n_seqs,), ctx_len, dtype=i32, device=dev)
+            pos = (start[seq.long()] + (torch.arange(n, device=dev) % per)).to(i32)
+            ctx = StepContext(rt=rt, n_tokens=n, n_seqs=n_seqs, tokens=seq, positions=pos, token_seq=seq, cu_seqlens=cu, slots=slots,
+                              start_pos=start, max_q_len=per, max_kv_len=ctx_len + per, is_decode=per == 1,
+                              total_kv_len=n_seqs * (ctx_len + per))
+            # the copies of the hidden state: update, read and norm in one pass, beside add + norm of one copy
+            copies, upd, w = rnd(n, S, H, dtype=f32), rnd(n, H, dtype=f32), rnd(H, dtype=f32)
+            mix, ow, iw = rnd(S, S, dtype=f32), rnd(S, dtype=f32), rnd(S, dtype=f32)
+            out = torch.empty(n, H, dtype=bf, device=dev)
+            add(f"hyper_norm, {S} copies ({tag})", n, timed(lambda: ops.hyper_norm(copies, w, 1e-5, out, update=upd, mix=mix, out_w=ow, in_w=iw)),
+                n * H * (8 * S + 4 + 2))
+            res, pend = rnd(n, H, dtype=f32), rnd(n, H)
+            add(f"add_rmsnorm ({tag})", n, timed(lambda: ops.add_rmsnorm(res, pend, w, 1e-5, out)), n * H * (4 + 4 + 2 + 2), like="hyper_norm")
+            # what stands between projection and attention, beside rotation and store of the Llama path
+            width = heads * hd + n_kv * (hd + vd) + heads
+            sums, bias = rnd(n, (width + 7) // 8 * 8, dtype=f32), rnd(width - heads, dtype=f32)
+            cs = rnd(n, m["rot"]["dims"] // 2, 2, dtype=f32)
+            q, gate = torch.empty(n, heads * hd, dtype=bf, device=dev), torch.empty(n, heads, dtype=f32, device=dev)
+            vf = rnd(n, n_kv * vd, dtype=f32)
+            add(f"qkv_finish ({tag})", n, timed(lambda: ops.qkv_finish(sums, bias, cs, heads, kv, q, seq, slots, pos, unit_norm=True, eps=1e-5,
+                                                                       v_first=vf, blend=0.3, gate_out=gate)),
+                n * (width * 4 + heads * hd * 2 + n_kv * (hd + vd) * 2 + n_kv * vd * 4))
+            qkv, cs2 = rnd(n, (heads + 2 * n_kv) * hd), rnd(n, hd // 2, 2, dtype=f32)
+            add(f"rope_kv_store ({tag})", n, timed(lambda: ops.rope_kv_store(qkv, cs2, heads, n_kv, hd, kv_like, seq, slots, pos)),
+                n * (heads + 2 * n_kv) * hd * 4, like="qkv_finish")
+            # attention within stretches, as the mixer runs it, beside the Llama path's at the same heads
+            keys = sum(min(i % chunk + 1, i + 1) for i in range(ctx_len, ctx_len + per)) * n_seqs
+            seen = min(ctx_len + per, chunk if per > 1 else ((ctx_len) % chunk + 1))
+            mixed = torch.empty(n, heads * vd, dtype=bf, device=dev)
+            att_bytes = n * heads * (hd + vd) * 2 + n_seqs * seen * n_kv * (hd + vd) * 2
+            add(f"attention within stretches of {chunk} ({tag})", n,
+                timed(lambda: ops.attention_general(q, mixed, kv, ctx, heads, hd ** -0.5, chunk=chunk, gate=gate)), att_bytes, 2 * heads * keys * (hd + vd))
+            narrow = torch.empty(n, heads * (hd // 2), dtype=bf, device=dev)
+            add(f"the same with values of {hd // 2} channels: attention_masked ({tag})", n,
+                timed(lambda: ops.attention_general(q, narrow, kv_narrow, ctx, heads, hd ** -0.5, chunk=chunk, gate=gate)),
+                n * heads * (hd + hd // 2) * 2 + n_seqs * seen * n_kv * (hd + hd // 2) * 2, 2 * heads * keys * (hd + hd // 2))
+            ql, ml = rnd(n, heads * hd), torch.empty(n, heads * hd, dtype=bf, device=dev)
+            if per == 1:
+                splits, chunk_pages, ring = ops.attention_decode_plan(n, heads, n_kv, hd, ctx_len + 1, 0, n * (ctx_len + 1))
+                scratch = torch.empty(max(1, ops.attention_decode_scratch_floats(n, heads, hd, splits)), dtype=f32, device=dev)
+                fn = lambda: ops.attention_decode_bf16(ql, ml, kv_like, slots, pos, heads, hd ** -0.5, 0, splits, scratch, chunk_pages=chunk_pages, ring_pages=ring)
+                like_keys, like_seen = n_seqs * (ctx_len + 1), ctx_len + 1
+            else:
+                fn = lambda: ops.attention_prefill_tcgen05(ql, ml, kv_like, cu, slots, start, n_seqs, per, heads, hd ** -0.5, 0)
+                like_keys, like_seen = per * (per + 1) // 2, per
+            add(f"attention over all keys, the Llama path ({tag})", n, timed(fn),
+                n * heads * hd * 4 + n_seqs * like_seen * n_kv * hd * 4, 2 * heads * like_keys * 2 * hd, like="attention within stretches")
+            # the experts, beside the gated experts of the Senupel path
+            x, router = rnd(n, H), rnd(E, H, dtype=f32)
+            chosen, wts = torch.empty(n, top, dtype=i32, device=dev), torch.empty(n, top, dtype=f32, device=dev)
+            add(f"moe_route, sigmoid scores ({tag})", n, timed(lambda: ops.moe_route(x, router, None, chosen, wts, "sigmoid")), n * H * 2 + E * H * 4)
+            add(f"moe_route, softmax over the chosen ({tag})", n, timed(lambda: ops.moe_route(x, router, None, chosen, wts)), n * H * 2 + E * H * 4, like="moe_route")
+            ops.moe_route(x, router, None, chosen, wts, "sigmoid")
+            tile = 128 if n * top >= 128 * E else 64
+            tiles = ops.moe_tiles_cap(n * top, E, tile)
+            row_item, item_row = torch.empty(tiles * tile, dtype=i32, device=dev), torch.empty(n * top, dtype=i32, device=dev)
+            tile_expert = torch.empty(tiles, dtype=i32, device=dev)
+            ops.moe_arrange(chosen, E, row_item, item_row, tile_expert, tile)
+            gathered = torch.empty(tiles * tile, H, dtype=bf, device=dev)
+            add(f"moe_gather, rows times their scores ({tag})", n, timed(lambda: ops.moe_gather(x, row_item, top, gathered, weights=wts)), n * H * 2 + n * top * H * 2)
+            add(f"moe_gather ({tag})", n, timed(lambda: ops.moe_gather(x, row_item, top, gathered)), n * H * 2 + n * top * H * 2, like="moe_gather")
+            wu, wgu, wd = rnd(E, eff, H), rnd(E, 2 * eff, H), rnd(E, H, eff)
+            acts, y = torch.empty(tiles * tile, eff, dtype=bf, device=dev), torch.empty(tiles * tile, H, dtype=f32, device=dev)
+            used = min(E, n * top)
+            add(f"moe_product up, squared relu ({tag})", n, timed(lambda: ops.moe_product(gathered, row_item, 0, wu, tile_expert, acts, epilogue="relu2")),
+                used * eff * H * 2 + n * top * (H + eff) * 2, 2 * n * top * eff * H)
+            add(f"moe_product gate, up, silu ({tag})", n, timed(lambda: ops.moe_product(gathered, row_item, 0, wgu, tile_expert, acts, epilogue="swiglu")),
+                used * 2 * eff * H * 2 + n * top * (H + eff) * 2, 2 * n * top * 2 * eff * H, like="moe_product up")
+            add(f"moe_product down ({tag})", n, timed(lambda: ops.moe_product(acts, row_item, 0, wd, tile_expert, y)),
+                used * eff * H * 2 + n * top * (eff * 2 + H * 4), 2 * n * top * eff * H)
+            outf = torch.empty(n, H, dtype=f32, device=dev)
+            add(f"moe_combine, plain sum ({tag})", n, timed(lambda: ops.moe_combine(y, item_row, None, outf)), n * top * H * 4 + n * H * 4)
+            add(f"moe_combine, weighted ({tag})", n, timed(lambda: ops.moe_combine(y, item_row, wts, outf)), n * top * H * 4 + n * H * 4, like="moe_combine")
+            del cache
+        return rows
+
     def kernel_table(cfg):
         """Each kernel the design added, alone, at this size: a prompt of T tokens and a
         decode step of 64 sequences; bytes it has to move / time / the copy peak.  Beside
@@ -773,7 +910,7 @@ def run_design(args):
     sampler.mark()
     sizes = {}
     design_sizes, what = DESIGNS[args.design]
-    table = senupel_kernel_table if args.design == "senupel" else kernel_table
+    table = {"senupel": senupel_kernel_table, "zotolix": zotolix_kernel_table}.get(args.design, kernel_table)
     for name in (args.sizes.split(",") if args.sizes else list(design_sizes)):
         design_cfg, llama_cfg = design_sizes[name]
         sizes[name] = {args.design: model_numbers(design_cfg), "llama": model_numbers(llama_cfg),

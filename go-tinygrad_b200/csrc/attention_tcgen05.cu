@@ -190,7 +190,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ block_table, int table_stride,
                             const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                             const int* __restrict__ start_pos,
-                            int n_heads, int n_kv, float scale, int window) {
+                            int n_heads, int n_kv, float scale, int window, int chunk,
+                            const float* __restrict__ gate) {
     using S = Shape<HD>;
     constexpr int BK = S::BK;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -217,7 +218,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int* table = block_table + (size_t)slots[b] * table_stride;
     const int rows_here = min(BQ, q_len - tile * BQ);
     const int k_max = start + tile * BQ + rows_here - 1;         // last key any row of the tile sees
-    const int k_min = window > 0 ? max(0, start + tile * BQ - window + 1) : 0;
+    // the first key the tile's first row sees: the window's edge, or the start of that row's stretch
+    // of `chunk` positions (stretches are counted from the sequence's first token)
+    int k_min = window > 0 ? max(0, start + tile * BQ - window + 1) : 0;
+    if (chunk > 0) k_min = max(k_min, (start + tile * BQ) - (start + tile * BQ) % chunk);
     const int j_lo = k_min / kPageTokens, j_hi = k_max / kPageTokens;
     const int n_steps = (j_hi - j_lo + S::kPages) / S::kPages;
 
@@ -310,6 +314,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const unsigned full = 0xffffffffu;
         const int r = warp * 32 + lane;                          // row of the tile, TMEM lane
         const int pos = start + tile * BQ + r;                   // position of this query
+        const int seen_from = chunk > 0 ? pos - pos % chunk : 0; // first key of this query's stretch
         const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
         const float sl2 = scale * kLog2e;
         float m_run = -INFINITY, l_run = 0.f;
@@ -326,12 +331,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free);                  // S_i is in registers: the tile takes S_{i+1}
-            const bool all_visible = (key0 + BK - 1 <= pos) && (window <= 0 || key0 > pos - window);
+            const bool all_visible = (key0 + BK - 1 <= pos) && (window <= 0 || key0 > pos - window) && key0 >= seen_from;
             if (!all_visible) {
 #pragma unroll
                 for (int c = 0; c < BK; ++c) {
                     const int key = key0 + c;
-                    const bool vis = key <= pos && (window <= 0 || key > pos - window);
+                    const bool vis = key <= pos && (window <= 0 || key > pos - window) && key >= seen_from;
                     if (!vis) sv[c] = __float_as_uint(-INFINITY);
                 }
             }
@@ -408,7 +413,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok) ok = __all_sync(full, mbar_wait<kTest>(pv_done, (uint32_t)(n_steps - 1) & 1u, abort_flag));
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            const float factor = (gate && r < rows_here) ? gate[(size_t)(q_begin + tile * BQ + r) * n_heads + h] : 1.0f;
+            const float inv = l_run > 0.f ? factor / l_run : 0.f;
             bf16* dst = out + (size_t)(q_begin + tile * BQ + r) * ldo + h * HD;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
@@ -469,7 +475,7 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long l
 template <int HD, bool kTest>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, bf16* out, int ldo, const int* block_table,
            int table_stride, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int max_q_len,
-           int n_heads, int n_kv, float scale, int window, cudaStream_t stream) {
+           int n_heads, int n_kv, float scale, int window, int chunk, const float* gate, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, kTest>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -480,7 +486,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, bf16* out, int l
     dim3 grid(n_heads, B, (max_q_len + BQ - 1) / BQ);
     return launch_chained(attention_prefill_tc_kernel<HD, kTest>, grid, dim3(kThreads), (size_t)Shape<HD>::kSmemBytes, stream,
                           map_q, map_kv, out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos,
-                          n_heads, n_kv, scale, window);
+                          n_heads, n_kv, scale, window, chunk, gate);
 }
 }  // namespace
 
@@ -501,8 +507,9 @@ GTG_API int gtg_attention_prefill_tcgen05(const void* q, int ldq, int n_tokens, 
                                           const int* block_table, int table_stride,
                                           const int* cu_seqlens, const int* slots, const int* start_pos,
                                           int B, int max_q_len, int n_heads, int n_kv, int hd,
-                                          float scale, int window, cudaStream_t stream) {
+                                          float scale, int window, int chunk, const float* gate, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return 0;
+    if (window < 0 || chunk < 0) return kErrBadArgument;
     if (hd != 64 && hd != 128) return kErrUnsupported;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return kErrBadArgument;
     if (ldq % 8 || ldo % 8 || ((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)kc % 16)) return kErrUnsupported;
@@ -517,7 +524,7 @@ GTG_API int gtg_attention_prefill_tcgen05(const void* q, int ldq, int n_tokens, 
     st = make_map(&map_kv, kc, (long long)n_pages * kv_rows, hd, hd, kPageTokens);
     if (st != 0) return st;
 #define GTG_ARGS map_q, map_kv, (bf16*)out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos, \
-                 B, max_q_len, n_heads, n_kv, scale, window, stream
+                 B, max_q_len, n_heads, n_kv, scale, window, chunk, gate, stream
     if (g_test_waits) return hd == 64 ? launch<64, true>(GTG_ARGS) : launch<128, true>(GTG_ARGS);
     return hd == 64 ? launch<64, false>(GTG_ARGS) : launch<128, false>(GTG_ARGS);
 #undef GTG_ARGS

@@ -181,6 +181,7 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
                     const int n2 = n0 + wn * 32 + j * 8 + t * 2;
                     if (pairs && n2 + 1 < N) {
                         float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
+                        if (epilogue >= kEpiActivation) { v0 = activate(v0, epilogue - kEpiActivation); v1 = activate(v1, epilogue - kEpiActivation); }
                         if (epilogue == 2) {
                             const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(G + m * ldg + n2));
                             v0 *= 1.0f / (1.0f + expf(-gg.x));
@@ -194,6 +195,7 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
                         const int n = n0 + wn * 32 + j * 8 + t * 2 + e;
                         if (n >= N) continue;
                         float v = acc[i][j][half * 2 + e];
+                        if (epilogue >= kEpiActivation) v = activate(v, epilogue - kEpiActivation);
                         if (epilogue == 2) v *= 1.0f / (1.0f + expf(-__bfloat162float(G[m * ldg + n])));
                         put<OutT>(C + m * ldc + n, v);
                     }
@@ -229,7 +231,8 @@ GTG_API int gtg_gemm_bf16_grouped(const void* A, int lda, long long batch_a, con
                                   long long batch_c, int out_f32, int batch, int M, int N, int K, int tile_rows,
                                   int epilogue, const void* G, int ldg, long long batch_g, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || batch <= 0) return 0;
-    if (K <= 0 || lda < K || ldw < K || epilogue < 0 || epilogue > 2 || (epilogue == 2 && !G)) return kErrBadArgument;
+    if (K <= 0 || lda < K || ldw < K || epilogue < 0 || (epilogue > 2 && !(epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations)) ||
+        (epilogue == 2 && !G)) return kErrBadArgument;
     if (K % 8 || lda % 8 || ldw % 8 || batch_a % 8 || batch_w % 8 || ((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     if (epilogue == 1 && N % 16) return kErrUnsupported;
     if (tile_expert && batch != 1) return kErrBadArgument;

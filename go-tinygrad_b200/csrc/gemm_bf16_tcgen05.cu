@@ -622,7 +622,8 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
 GTG_API int gtg_gemm_bf16_tcgen05_grouped(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
                                           int out_f32, int M, int N, int K, int epilogue, const int* tile_expert,
                                           int n_experts, cudaStream_t stream) {
-    if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
+    if (epilogue != 0 && epilogue != 1 && !(epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations))
+        return kErrBadArgument;
     if (!tile_expert || n_experts <= 0 || M % BM) return kErrBadArgument;
     if ((long long)N * n_experts > 0x7fffffffLL) return kErrUnsupported;
     return run(A, lda, W, ldw, C, ldc, out_f32, M, N, K, epilogue, RopeKV{}, stream, Grouping{tile_expert, N}, n_experts);

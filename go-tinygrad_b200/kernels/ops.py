@@ -101,7 +101,7 @@ _SIGNATURES = {
     "gtg_attention_tcgen05_supports": ("attention_tcgen05", [_I]),
     "gtg_attention_tcgen05_status": ("attention_tcgen05", []),
     "gtg_attention_prefill_tcgen05": ("attention_tcgen05", [_P, _I, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P,
-                                                            _I, _I, _I, _I, _I, _F, _I, _P]),
+                                                            _I, _I, _I, _I, _I, _F, _I, _I, _P, _P]),
     "gtg_argmax": ("sampling", [_P, _I, _I, _I, _P, _P]),
     "gtg_sample_temperature": ("sampling", [_P, _I, _I, _I, _F, _U, _P, _P, _P, _P]),
 }
@@ -919,7 +919,13 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kv, ctx, n_heads: int,
     step's context (rows, positions, sequences).  out[n, h] = gate[n, h] *
     softmax(q . K * scale over the visible keys) V.  bfloat16 heads of a multiple of 8
     channels up to 128 take the tensor-core kernel (`attention_masked_bf16`); float32
-    and other widths the plain one."""
+    and other widths the plain one; steps that bring more than one token a sequence, with
+    keys and values of 64 or 128 channels alike, the prompt attention on tcgen05."""
+    if (q.dtype == torch.bfloat16 and not ctx.is_decode and kv.value_dim == kv.head_dim and attention_tcgen05_supports(kv)
+            and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
+        attention_prefill_tcgen05(q, out, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, ctx.n_seqs, ctx.max_q_len, n_heads, scale,
+                                  window, chunk, gate)
+        return
     if q.dtype == torch.bfloat16 and attention_masked_supports(kv) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and scale > 0:
         splits = int(_fn("gtg_attention_masked_splits")(ctx.n_seqs, ctx.max_q_len, n_heads, kv.n_kv_heads, ctx.max_kv_len,
                                                         int(window), int(chunk)))
@@ -990,9 +996,14 @@ def attention_tcgen05_supports(kv) -> bool:
 
 
 def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int, max_q_len: int,
-                              n_heads: int, scale: float, window: int = 0) -> None:
-    """Prompt attention on tcgen05 (128 queries x one head per thread block)."""
+                              n_heads: int, scale: float, window: int = 0, chunk: int = 0,
+                              gate: Optional[torch.Tensor] = None) -> None:
+    """Prompt attention on tcgen05 (128 queries x one head per thread block).  `chunk` > 0:
+    a query sees the keys of its own stretch of `chunk` positions only; `gate`: float32
+    [N, n_heads], a factor on each head's output."""
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (q.shape[0], n_heads)),
+          "attention: gate must be contiguous float32 [N, n_heads]")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "attention_prefill_tcgen05: bfloat16 only")
     _need(attention_tcgen05_supports(kv),
           "attention_prefill_tcgen05: needs head_dim 64 or 128 and keys and values of a page side by side")
@@ -1001,7 +1012,8 @@ def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: 
                                                 _ptr(kv.k), _ptr(kv.v), kv.page_stride, kv.k.shape[0],
                                                 _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens),
                                                 _ptr(slots), _ptr(start_pos), n_seqs, max_q_len, n_heads,
-                                                kv.n_kv_heads, kv.head_dim, float(scale), int(window), _stream()),
+                                                kv.n_kv_heads, kv.head_dim, float(scale), int(window), int(chunk),
+                                                _ptr(gate), _stream()),
            "attention_prefill_tcgen05")
 
 
@@ -1296,36 +1308,39 @@ def moe_product(a: torch.Tensor, row_item: torch.Tensor, item_div: int, w: torch
     rows: `moe_gather`), which in tiles of 128 takes the prompt-sized tensor-memory
     product.  w [E, N, K].  The tile is out's rows over tile_expert's length: 64, or 128 on the tensor
     cores.  epilogue="swiglu" (tensor cores only: `moe_product_fused_supports`):
-    every w[e] is laid out by `interleave_gate_up` and out [rows, N/2] = silu(gate) * up."""
+    every w[e] is laid out by `interleave_gate_up` and out [rows, N/2] = silu(gate) * up.
+    epilogue="relu2" | "gelu_tanh" | "silu": that activation of the product, applied to the float
+    sums inside the tensor-core kernels, by the `activation` kernel behind the plain one."""
     _rows2d(a, "moe_product: a"); _rows2d(out, "moe_product: out")
     E, N, K = w.shape
     cap = tile_expert.numel()
     tile = out.shape[0] // max(cap, 1)
     _need(epilogue in ("none", "swiglu") or epilogue in ACTIVATIONS, f"moe_product: unknown epilogue {epilogue!r}")
-    if epilogue in ACTIVATIONS:
-        # an activation of the product: on the float sums where the kernel has the epilogue, else behind it
+    if epilogue in ACTIVATIONS and not moe_product_fused_supports(a, w):
+        # the plain product has no epilogue: the activation runs behind it
         moe_product(a, row_item, item_div, w, tile_expert, out)
         activation(out, epilogue)
         return
     n_out = N // 2 if epilogue == "swiglu" else N
+    epi_code = 1 if epilogue == "swiglu" else EPILOGUE_ACTIVATION + ACTIVATIONS[epilogue] if epilogue in ACTIVATIONS else 0
     _need(w.is_contiguous() and a.dtype == w.dtype and a.shape[1] == K, "moe_product: a [*, K] and contiguous w [E, N, K] of one dtype")
     _need(tuple(out.shape) == (cap * tile, n_out) and out.dtype in (a.dtype, torch.float32), "moe_product: out must be [tiles * tile, N]")
     _need(item_div > 0 or a.shape[0] == out.shape[0], "moe_product: a must hold the arranged rows")
     _int32("moe_product", row_item, tile_expert)
     if moe_product_fused_supports(a, w):
         _need(tile in (64, 128), f"moe_product: tiles of 64 or 128 rows, not {tile}")
-        _need(epilogue == "none" or N % 16 == 0, "moe_product: the fused gated silu needs a multiple of 16 rows per expert")
+        _need(epilogue != "swiglu" or N % 16 == 0, "moe_product: the fused gated silu needs a multiple of 16 rows per expert")
         if (tile == 128 and item_div == 0 and out.data_ptr() % 16 == 0
                 and out.stride(0) % (4 if out.dtype == torch.float32 else 8) == 0):
             # arranged rows in tiles of 128: the prompt-sized product (tensor copies, tensor memory)
             _check(_fn("gtg_gemm_bf16_tcgen05_grouped")(_ptr(a), a.stride(0), _ptr(w), K, _ptr(out), out.stride(0),
                                                         1 if out.dtype == torch.float32 else 0, cap * tile, N, K,
-                                                        1 if epilogue == "swiglu" else 0, _ptr(tile_expert), E, _stream()),
+                                                        epi_code, _ptr(tile_expert), E, _stream()),
                    "moe_product(tcgen05)")
             return
         _check(_fn("gtg_gemm_bf16_grouped")(_ptr(a), a.stride(0), 0, _ptr(row_item), int(item_div), _ptr(w), K, N * K,
                                             _ptr(tile_expert), _ptr(out), out.stride(0), 0, 1 if out.dtype == torch.float32 else 0,
-                                            1, cap * tile, N, K, tile, 1 if epilogue == "swiglu" else 0, None, 0, 0, _stream()),
+                                            1, cap * tile, N, K, tile, epi_code, None, 0, 0, _stream()),
                "moe_product(bfloat16)")
         return
     _need(epilogue == "none" and tile == MOE_TILE_ROWS, "moe_product: the plain product has tiles of 64 rows and no epilogue")
