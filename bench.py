@@ -740,7 +740,7 @@ def run_design(args):
 
     def zotolix_kernel_table(cfg):
         """Each kernel the Zotolix design added or extended, alone, at this size: a prompt of T
-        tokens and a decode step of 64 sequences after 1,024 tokens; the bytes it has to move
+        tokens and a decode step of 64 sequences at the last place of a stretch; the bytes it has to move
         against the copy peak and, for products and attention, its FLOPs against the matrix
         peak.  Beside each the like kernel of the Llama path (of the Senupel path for the
         experts) at the same rows."""
@@ -758,7 +758,8 @@ def run_design(args):
                          **({"tflops": round(flops / ms / 1e9, 1), "of_matrix_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)} if flops else {}),
                          **({"like": like} if like else {})})
         rnd = lambda *shape, dtype=bf: torch.randn(*shape, device=dev, dtype=f32).to(dtype)
-        for n, n_seqs, ctx_len, tag in ((T, 1, 0, "prompt"), (64, 64, prompt_len, "decode")):
+        # the decode step stands at the last place of a stretch, where it sees the most keys
+        for n, n_seqs, ctx_len, tag in ((T, 1, 0, "prompt"), (64, 64, max(prompt_len, chunk) // chunk * chunk - 1, "decode")):
             per = n // n_seqs
             rt = lib.parts.Runtime(dev, bf)
             cache = Cache([[KVRequest(n_kv, hd, None, value_dim=vd, chunk=chunk)], [KVRequest(n_kv, hd, None)],

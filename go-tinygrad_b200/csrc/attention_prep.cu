@@ -17,6 +17,10 @@
 #include <math.h>
 
 namespace {
+// two neighbouring channels in one access (the address is a multiple of two elements)
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 qkv_finish_kernel(const float* __restrict__ sums, int ld, const float* __restrict__ bias,
@@ -30,14 +34,30 @@ qkv_finish_kernel(const float* __restrict__ sums, int ld, const float* __restric
                   int n_heads, int n_kv, int hd, int vd, int has_gate) {
     chain_release();
     chain_wait();
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const int q_w = n_heads * hd, k_w = n_kv * hd, v_w = n_kv * vd;
     const int biased = q_w + k_w + v_w;
     const int width = biased + (has_gate ? n_heads : 0);
     const float* src = sums + (size_t)n * ld;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = src[i] + ((bias && i < biased) ? bias[i] : 0.f);
+    if (ld % 4 == 0 && (reinterpret_cast<uintptr_t>(sums) % 16) == 0) {
+        // four sums an access; the biases are the same for every token and come from the caches
+        const int whole = width & ~3;
+        for (int i = threadIdx.x * 4; i < whole; i += blockDim.x * 4) {
+            float4 t = *reinterpret_cast<const float4*>(src + i);
+            if (bias) {
+                if (i + 0 < biased) t.x += __ldg(bias + i + 0);
+                if (i + 1 < biased) t.y += __ldg(bias + i + 1);
+                if (i + 2 < biased) t.z += __ldg(bias + i + 2);
+                if (i + 3 < biased) t.w += __ldg(bias + i + 3);
+            }
+            *reinterpret_cast<float4*>(row + i) = t;
+        }
+        for (int i = whole + threadIdx.x; i < width; i += blockDim.x) row[i] = src[i] + ((bias && i < biased) ? bias[i] : 0.f);
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = src[i] + ((bias && i < biased) ? bias[i] : 0.f);
+    }
     __syncthreads();
 
     const int pos = positions[n];
@@ -69,10 +89,31 @@ qkv_finish_kernel(const float* __restrict__ sums, int ld, const float* __restric
         if (head < n_heads) dst = q_out + (size_t)n * ldq + (size_t)head * hd;
         else if (kc) dst = kc + page_off + ((size_t)(head - n_heads) * kPageTokens + (pos % kPageTokens)) * hd;
         else continue;
-        for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(x[i] * inv);
+        if (hd % 2 == 0 && (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(T))) == 0) {
+            for (int i = lane * 2; i < hd; i += 64) store_pair(dst + i, x[i] * inv, x[i + 1] * inv);
+        } else {
+            for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(x[i] * inv);
+        }
     }
     // values
     const float* v = row + q_w + k_w;
+    const bool v_pairs = vd % 2 == 0 && (q_w + k_w) % 2 == 0 && (!vc || (page_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(vc) % (2 * sizeof(T))) == 0)) &&
+                         (!v_keep || (reinterpret_cast<uintptr_t>(v_keep) % 8) == 0) && (!v_first || (reinterpret_cast<uintptr_t>(v_first) % 8) == 0);
+    if (v_pairs) {
+        for (int i = threadIdx.x * 2; i < v_w; i += blockDim.x * 2) {
+            float2 val = *reinterpret_cast<const float2*>(v + i);
+            if (v_keep) *reinterpret_cast<float2*>(v_keep + (size_t)n * v_w + i) = val;
+            if (v_first) {
+                const float2 f = *reinterpret_cast<const float2*>(v_first + (size_t)n * v_w + i);
+                val.x = (1.0f - lambda) * val.x + lambda * f.x;
+                val.y = (1.0f - lambda) * val.y + lambda * f.y;
+            }
+            if (vc) {
+                const int head = i / vd, c = i - head * vd;
+                store_pair(vc + page_off + ((size_t)head * kPageTokens + (pos % kPageTokens)) * vd + c, val.x, val.y);
+            }
+        }
+    } else
     for (int i = threadIdx.x; i < v_w; i += blockDim.x) {
         float val = v[i];
         if (v_keep) v_keep[(size_t)n * v_w + i] = val;

@@ -27,45 +27,85 @@
 
 namespace {
 // ---- route ----------------------------------------------------------------------
-// One block of eight warps per token: the token's row is staged in shared memory as
-// float, every warp takes every eighth expert (lanes striding over the channels, the
-// router's rows read coalesced), and thread 0 picks from the logits.
-template <typename T>
+// One block of eight warps per TB tokens: the tokens' rows are staged in shared memory as
+// they are, every warp takes every eighth expert (lanes striding over the channels, the
+// router's rows read coalesced, each value read once for all TB tokens; products and sums
+// in float), and one thread a token picks from the logits.  A token's sums are added in the
+// same order whatever TB is.
+__device__ __forceinline__ float4 four_channels(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 four_channels(const bf16* p) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename T, int TB>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, const float* __restrict__ bias,
                  int* __restrict__ chosen, float* __restrict__ weights, int N, int H, int E, int top, int scoring) {
     chain_release();
     chain_wait();
-    extern __shared__ float smem[];
-    float* xs = smem;            // [H]
-    float* z = smem + H;         // [E]
+    extern __shared__ __align__(16) unsigned char route_smem[];
+    constexpr int kPer16 = 16 / (int)sizeof(T);          // channels in 16 bytes
+    const int Hp = (H + kPer16 - 1) / kPer16 * kPer16;   // a staged row, whole 16 bytes
+    T* xs = reinterpret_cast<T*>(route_smem);            // [TB][Hp]
+    float* zs = reinterpret_cast<float*>(route_smem + (size_t)TB * Hp * sizeof(T));   // [TB][2 E]: logits, then the chosen scores
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x;
-    const T* xr = x + (size_t)n * ldx;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = to_f32<T>(xr[i]);
+    const int n0 = blockIdx.x * TB;
+    const int nt = min(TB, N - n0);
+    const bool wide_rows = H % kPer16 == 0 && ldx % kPer16 == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0;
+#pragma unroll
+    for (int t = 0; t < TB; ++t) {
+        const T* xr = x + (size_t)(n0 + t) * ldx;
+        T* dst = xs + (size_t)t * Hp;
+        if (t >= nt) {
+            for (int i = threadIdx.x; i < Hp; i += blockDim.x) dst[i] = from_f32<T>(0.f);
+        } else if (wide_rows) {
+            for (int i = threadIdx.x; i < H / kPer16; i += blockDim.x)
+                reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(xr)[i];
+        } else {
+            for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = xr[i];
+        }
+    }
     __syncthreads();
     const int n_warps = blockDim.x >> 5;
     for (int e = warp; e < E; e += n_warps) {
         // a warp an expert: two chains over alternate steps, four channels a lane and step where the row allows it,
         // the loads of several steps in flight together
         const float* r = router + (size_t)e * H;
-        float s0 = 0.f, s1 = 0.f;
+        float s0[TB], s1[TB];
+#pragma unroll
+        for (int t = 0; t < TB; ++t) s0[t] = s1[t] = 0.f;
         if (H % 256 == 0 && (reinterpret_cast<uintptr_t>(router) % 16) == 0) {
 #pragma unroll 4
             for (int i = lane * 4; i < H; i += 256) {
-                const float4 v0 = *reinterpret_cast<const float4*>(xs + i), v1 = *reinterpret_cast<const float4*>(xs + i + 128);
                 const float4 a = *reinterpret_cast<const float4*>(r + i), b = *reinterpret_cast<const float4*>(r + i + 128);
-                s0 = fmaf(v0.x, a.x, s0); s0 = fmaf(v0.y, a.y, s0); s0 = fmaf(v0.z, a.z, s0); s0 = fmaf(v0.w, a.w, s0);
-                s1 = fmaf(v1.x, b.x, s1); s1 = fmaf(v1.y, b.y, s1); s1 = fmaf(v1.z, b.z, s1); s1 = fmaf(v1.w, b.w, s1);
+#pragma unroll
+                for (int t = 0; t < TB; ++t) {
+                    const float4 v0 = four_channels(xs + (size_t)t * Hp + i), v1 = four_channels(xs + (size_t)t * Hp + i + 128);
+                    s0[t] = fmaf(v0.x, a.x, s0[t]); s0[t] = fmaf(v0.y, a.y, s0[t]); s0[t] = fmaf(v0.z, a.z, s0[t]); s0[t] = fmaf(v0.w, a.w, s0[t]);
+                    s1[t] = fmaf(v1.x, b.x, s1[t]); s1[t] = fmaf(v1.y, b.y, s1[t]); s1[t] = fmaf(v1.z, b.z, s1[t]); s1[t] = fmaf(v1.w, b.w, s1[t]);
+                }
             }
         } else {
-            for (int i = lane; i < H; i += 32) s0 = fmaf(xs[i], r[i], s0);
+            for (int i = lane; i < H; i += 32) {
+                const float rv = r[i];
+#pragma unroll
+                for (int t = 0; t < TB; ++t) s0[t] = fmaf(to_f32<T>(xs[(size_t)t * Hp + i]), rv, s0[t]);
+            }
         }
-        s0 = warp_sum(s0 + s1);
-        if (lane == 0) z[e] = s0 + (bias ? bias[e] : 0.f);
+#pragma unroll
+        for (int t = 0; t < TB; ++t) {
+            const float sum = warp_sum(s0[t] + s1[t]);
+            if (lane == 0) zs[t * 2 * E + e] = sum + (bias ? bias[e] : 0.f);
+        }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < nt) {
+        const int n = n0 + threadIdx.x;
+        float* z = zs + threadIdx.x * 2 * E;
+        float* kept = z + E;
         // top <= E rounds of a first-maximum search; a chosen logit becomes NaN, which no comparison picks again
         float best0 = 0.f, total = 0.f;
         for (int k = 0; k < top; ++k) {
@@ -80,11 +120,11 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
             if (k == 0) best0 = best;
             chosen[(size_t)n * top + k] = arg;
             const float p = scoring == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - best0);
-            xs[k] = p;                                      // the staged row is no longer needed (top <= E <= H is checked)
+            kept[k] = p;
             total += p;
         }
         const float inv = scoring == 1 ? 1.0f : 1.0f / total;
-        for (int k = 0; k < top; ++k) weights[(size_t)n * top + k] = xs[k] * inv;
+        for (int k = 0; k < top; ++k) weights[(size_t)n * top + k] = kept[k] * inv;
     }
 }
 
@@ -217,6 +257,32 @@ __global__ void moe_gather_scaled_kernel(const T* __restrict__ x, int ldx, const
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = from_f32<T>(w * to_f32<T>(src[i]));
 }
 
+// bfloat16 rows of a multiple of 8 channels, 16 bytes an access: each channel is widened, multiplied
+// in float and rounded once, as in the kernel above.
+__global__ void moe_gather_scaled_wide_kernel(const bf16* __restrict__ x, int ldx, const int* __restrict__ row_item, int item_div,
+                                              const float* __restrict__ weights, bf16* __restrict__ out, int H8) {
+    chain_release();
+    chain_wait();
+    const int item = row_item[blockIdx.x];
+    uint4* dst = reinterpret_cast<uint4*>(out) + (size_t)blockIdx.x * H8;
+    if (item < 0) {
+        for (int i = threadIdx.x; i < H8; i += blockDim.x) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const float w = weights ? weights[item] : 1.0f;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(item / item_div) * ldx);
+    for (int i = threadIdx.x; i < H8; i += blockDim.x) {
+        uint4 t = src[i];
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            h[e] = __floats2bfloat162_rn(w * f.x, w * f.y);
+        }
+        dst[i] = t;
+    }
+}
+
 // ---- combine ----------------------------------------------------------------------
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, int ldy, const int* __restrict__ item_row,
@@ -237,12 +303,26 @@ GTG_API int gtg_moe_route(int dtype, const void* x, int ldx, const float* router
                           float* weights, int N, int H, int E, int top, int scoring, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || H <= 0 || scoring < 0 || scoring > 1) return kErrBadArgument;
-    if (top > H) return kErrUnsupported;
-    const size_t smem = (size_t)(H + E) * sizeof(float);
-    if (smem > 48 * 1024) return kErrUnsupported;
-    const dim3 grid(N);
-    if (dtype == 0) return launch_chained(moe_route_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, ldx, router, bias, chosen, weights, N, H, E, top, scoring);
-    if (dtype == 1) return launch_chained(moe_route_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)x, ldx, router, bias, chosen, weights, N, H, E, top, scoring);
+    // many tokens: four share a block, so that the router is read a quarter as often
+    const size_t elem = dtype == 0 ? 4 : 2;
+    const size_t row = ((size_t)H * elem + 15) / 16 * 16;
+    const int tb = (N >= 1024 && 4 * (row + 2 * (size_t)E * sizeof(float)) <= 64 * 1024) ? 4 : 1;
+    const size_t smem = tb * (row + 2 * (size_t)E * sizeof(float));
+    if (smem > 160 * 1024) return kErrUnsupported;
+    const dim3 grid((N + tb - 1) / tb);
+#define GTG_ROUTE(T, TB)                                                                                           \
+    do {                                                                                                           \
+        auto kernel = moe_route_kernel<T, TB>;                                                                     \
+        if (smem > 48 * 1024) {                                                                                    \
+            const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                                   \
+        }                                                                                                          \
+        return launch_chained(kernel, grid, dim3(256), smem, stream, (const T*)x, ldx, router, bias, chosen, weights, \
+                              N, H, E, top, scoring);                                                              \
+    } while (0)
+    if (dtype == 0) { if (tb == 4) GTG_ROUTE(float, 4); else GTG_ROUTE(float, 1); }
+    if (dtype == 1) { if (tb == 4) GTG_ROUTE(bf16, 4); else GTG_ROUTE(bf16, 1); }
+#undef GTG_ROUTE
     return kErrBadArgument;
 }
 
@@ -298,6 +378,8 @@ GTG_API int gtg_moe_gather_scaled(int dtype, const void* x, int ldx, const int* 
     if (rows <= 0) return 0;
     if (H <= 0 || item_div <= 0) return kErrBadArgument;
     if (dtype == 0) return launch_chained(moe_gather_scaled_kernel<float>, dim3(rows), dim3(128), 0, stream, (const float*)x, ldx, row_item, item_div, weights, (float*)out, H);
+    if (dtype == 1 && H % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0)
+        return launch_chained(moe_gather_scaled_wide_kernel, dim3(rows), dim3(128), 0, stream, (const bf16*)x, ldx, row_item, item_div, weights, (bf16*)out, H / 8);
     if (dtype == 1) return launch_chained(moe_gather_scaled_kernel<bf16>, dim3(rows), dim3(128), 0, stream, (const bf16*)x, ldx, row_item, item_div, weights, (bf16*)out, H);
     return kErrBadArgument;
 }
