@@ -18,7 +18,9 @@
 #include "mma_helpers.cuh"
 
 namespace {
-constexpr int BN = 128, BK = 32, STAGES = 4;
+constexpr int BN = 128;
+// BK, the channels of k a stage holds, is 32 or 64: arranged rows of few tokens an expert (decode steps) are all
+// weight streaming, and stages of 64 channels ask for a weight row's bytes a whole 128-byte line at a time.
 constexpr int kThreads = 256;
 
 template <typename OutT>
@@ -35,7 +37,7 @@ template <> __device__ __forceinline__ void put2<float>(float* p, float v0, floa
     *reinterpret_cast<float2*>(p) = make_float2(v0, v1);
 }
 
-template <int BM, typename OutT>
+template <int BM, int BK, int STAGES, typename OutT>
 __global__ void __launch_bounds__(kThreads)
 grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const int* __restrict__ row_item, int item_div,
                    const bf16* __restrict__ W, int ldw, long long batch_w, const int* __restrict__ tile_expert,
@@ -45,6 +47,7 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
     chain_wait();
     constexpr int MI = BM / 32;                        // 16-row fragments per warp (2 x 4 warps)
     constexpr int kStageBytes = (BM + BN) * BK * 2;
+    constexpr int CPR = BK / 8;                        // 16-byte chunks per staged row
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int src[BM];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -78,18 +81,18 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
         const uint32_t w_base = a_base + BM * BK * 2;
         const int k0 = kt * BK;
 #pragma unroll
-        for (int i = 0; i < BM * 4 / kThreads; ++i) {
+        for (int i = 0; i < BM * CPR / kThreads; ++i) {
             const int id = tid + i * kThreads;
-            const int r = id >> 2, c = id & 3;
+            const int r = id / CPR, c = id % CPR;
             const int k = k0 + c * 8;
             const int s = src[r];
             const bool ok = s >= 0 && k < K;
             cp_async16(a_base + swz_offset<BK>(r, c), ok ? A + (size_t)s * lda + k : A, ok ? 16 : 0);
         }
 #pragma unroll
-        for (int i = 0; i < BN * 4 / kThreads; ++i) {
+        for (int i = 0; i < BN * CPR / kThreads; ++i) {
             const int id = tid + i * kThreads;
-            const int r = id >> 2, c = id & 3;
+            const int r = id / CPR, c = id % CPR;
             const int k = k0 + c * 8;
             const int n = n0 + r;
             const bool ok = n < N && k < K;
@@ -205,20 +208,20 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
     }
 }
 
-template <int BM, typename OutT>
+template <int BM, int BK, int STAGES, typename OutT>
 int launch(const bf16* A, int lda, long long batch_a, const int* row_item, int item_div, const bf16* W, int ldw,
            long long batch_w, const int* tile_expert, OutT* C, int ldc, long long batch_c, int batch, int M, int N, int K,
            int epilogue, const bf16* G, int ldg, long long batch_g, cudaStream_t stream) {
     const int smem = STAGES * (BM + BN) * BK * 2;
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(grouped_mma_kernel<BM, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        const cudaError_t e = cudaFuncSetAttribute(grouped_mma_kernel<BM, BK, STAGES, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     if (grid.y > 65535 || grid.z > 65535) return kErrUnsupported;
-    return launch_chained(grouped_mma_kernel<BM, OutT>, grid, dim3(kThreads), (size_t)smem, stream, A, lda, batch_a, row_item,
+    return launch_chained(grouped_mma_kernel<BM, BK, STAGES, OutT>, grid, dim3(kThreads), (size_t)smem, stream, A, lda, batch_a, row_item,
                           item_div, W, ldw, batch_w, tile_expert, C, ldc, batch_c, M, N, K, epilogue, G, ldg, batch_g);
 }
 }  // namespace
@@ -236,11 +239,22 @@ GTG_API int gtg_gemm_bf16_grouped(const void* A, int lda, long long batch_a, con
     if (K % 8 || lda % 8 || ldw % 8 || batch_a % 8 || batch_w % 8 || ((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     if (epilogue == 1 && N % 16) return kErrUnsupported;
     if (tile_expert && batch != 1) return kErrBadArgument;
-#define GTG_GROUPED(BM, T)                                                                                          \
-    return launch<BM, T>((const bf16*)A, lda, batch_a, row_item, item_div, (const bf16*)W, ldw, batch_w, tile_expert, \
+#define GTG_GROUPED(BM, BK, ST, T)                                                                                  \
+    return launch<BM, BK, ST, T>((const bf16*)A, lda, batch_a, row_item, item_div, (const bf16*)W, ldw, batch_w, tile_expert, \
                          (T*)C, ldc, batch_c, batch, M, N, K, epilogue, (const bf16*)G, ldg, batch_g, stream)
-    if (tile_rows == 64) { if (out_f32) GTG_GROUPED(64, float); else GTG_GROUPED(64, bf16); }
-    if (tile_rows == 128) { if (out_f32) GTG_GROUPED(128, float); else GTG_GROUPED(128, bf16); }
+    if (tile_rows == 64 && tile_expert && K >= 256) {
+        // four stages (two blocks a multiprocessor) while all blocks are resident that way, else three (three blocks)
+        static int n_sm = 0;
+        if (n_sm == 0) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n_sm = 1;
+        }
+        const long long blocks = (long long)((N + BN - 1) / BN) * ((M + 63) / 64);
+        if (blocks <= 2LL * n_sm) { if (out_f32) GTG_GROUPED(64, 64, 4, float); else GTG_GROUPED(64, 64, 4, bf16); }
+        if (out_f32) GTG_GROUPED(64, 64, 3, float); else GTG_GROUPED(64, 64, 3, bf16);
+    }
+    if (tile_rows == 64) { if (out_f32) GTG_GROUPED(64, 32, 4, float); else GTG_GROUPED(64, 32, 4, bf16); }
+    if (tile_rows == 128) { if (out_f32) GTG_GROUPED(128, 32, 4, float); else GTG_GROUPED(128, 32, 4, bf16); }
 #undef GTG_GROUPED
     return kErrBadArgument;
 }
