@@ -243,14 +243,16 @@ GTG_API int gtg_gemm_bf16_grouped(const void* A, int lda, long long batch_a, con
     return launch<BM, BK, ST, T>((const bf16*)A, lda, batch_a, row_item, item_div, (const bf16*)W, ldw, batch_w, tile_expert, \
                          (T*)C, ldc, batch_c, batch, M, N, K, epilogue, (const bf16*)G, ldg, batch_g, stream)
     if (tile_rows == 64 && tile_expert && K >= 256) {
-        // four stages (two blocks a multiprocessor) while all blocks are resident that way, else three (three blocks)
+        // Four stages (two blocks a multiprocessor, which leaves room for the first blocks of the kernel behind it)
+        // up to three blocks a multiprocessor, counting the arrangement's spare tiles, which do not exist and end at
+        // once; beyond that three stages (three blocks a multiprocessor).  Measured both ways at either size.
         static int n_sm = 0;
         if (n_sm == 0) {
             int dev = 0;
             if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n_sm = 1;
         }
         const long long blocks = (long long)((N + BN - 1) / BN) * ((M + 63) / 64);
-        if (blocks <= 2LL * n_sm) { if (out_f32) GTG_GROUPED(64, 64, 4, float); else GTG_GROUPED(64, 64, 4, bf16); }
+        if (blocks <= 3LL * n_sm) { if (out_f32) GTG_GROUPED(64, 64, 4, float); else GTG_GROUPED(64, 64, 4, bf16); }
         if (out_f32) GTG_GROUPED(64, 64, 3, float); else GTG_GROUPED(64, 64, 3, bf16);
     }
     if (tile_rows == 64) { if (out_f32) GTG_GROUPED(64, 32, 4, float); else GTG_GROUPED(64, 32, 4, bf16); }
