@@ -500,7 +500,7 @@ def zotolix_shape(width, heads, kv_heads, dim, experts, expert_ff, top, vocab=32
                 "mask": {"size": 8192 if i % 2 else 1024}, "rot": {"dims": dim // 2, "base": 500000.0}}
     routed = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
     return {"architecture": "Zotolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 8.0},
-            "residual_mult": 0.5, "streams": 4,
+            "residual_mult": 0.8, "streams": 4,
             "layers": [{"type": "attention_2" if i % 2 else "attention", "mixer": mixer(i), "mlp": routed} for i in range(8)]}
 
 

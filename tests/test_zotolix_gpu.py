@@ -282,8 +282,8 @@ def _plain_rows(q, k, v, start, scale, chunk, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,hd,vd", [(4, 2, 128, 48), (8, 1, 64, 128), (3, 3, 24, 40), (6, 2, 16, 8), (2, 2, 128, 128),
-                                                  (5, 5, 20, 12), (12, 4, 8, 72)])
+@pytest.mark.parametrize("heads,kv_heads,hd,vd", [(6, 3, 128, 56), (8, 1, 64, 128), (3, 3, 24, 40), (6, 2, 16, 8), (2, 2, 128, 128),
+                                                  (5, 5, 20, 12), (12, 4, 8, 72), (8, 2, 64, 64)])
 @pytest.mark.parametrize("chunk,window", [(None, None), (1, None), (5, None), (64, None), (70, None), (200, None), (1000, None),
                                           (None, 70), (100, 33)])
 def test_attention_over_stretches_of_keys_in_prompts_portions_and_decode_steps(dtype, heads, kv_heads, hd, vd, chunk, window):
