@@ -1,8 +1,8 @@
 // What stands between the fused projection of an attention mixer and the
 // attention itself, for mixers whose projections have more to them than a
-// rotation: one block per token takes the projection's float sums
-//   [ q: n_heads x hd | k: n_kv x hd | v: n_kv x vd | g: n_heads ]
-// and, all in float,
+// rotation: of a token's float sums out of the projection,
+//   [ q: n_heads x hd | k: n_kv x hd | v: n_kv x vd | g: n_heads ],
+// a warp takes one head (or the gates) and, all in float,
 //   * adds the biases of q, k and v;
 //   * rotates the first `rot` channels of every query and key head, channel i with
 //     i + rot/2, by the token's (cos, sin) table; the rest of a head passes;
@@ -21,9 +21,11 @@ namespace {
 __device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
 __device__ __forceinline__ void store_pair(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
 
+// A block a token: the token's sums are staged in shared memory (all loads in flight at once), then a warp
+// takes a head at a time.  For the many tokens of a prompt.
 template <typename T>
 __global__ void __launch_bounds__(256)
-qkv_finish_kernel(const float* __restrict__ sums, int ld, const float* __restrict__ bias,
+qkv_finish_rows_kernel(const float* __restrict__ sums, int ld, const float* __restrict__ bias,
                   const float2* __restrict__ cos_sin, int rot, int unit_norm, float eps,
                   const float* __restrict__ v_first, float* __restrict__ v_keep, float lambda,
                   T* __restrict__ q_out, int ldq, float* __restrict__ gate_out,
@@ -127,6 +129,95 @@ qkv_finish_kernel(const float* __restrict__ sums, int ld, const float* __restric
         for (int h = threadIdx.x; h < n_heads; h += blockDim.x)
             gate_out[(size_t)n * n_heads + h] = 1.0f / (1.0f + expf(-row[biased + h]));
 }
+
+constexpr int kFinishWarps = 8;
+
+// A warp an item: a query head, a key head, a value head, or the token's gates; a token's items
+// are dealt to gridDim.y blocks of kFinishWarps warps and nothing meets across warps.  For the few
+// tokens of a decode step or a short portion, which a block a token leaves most of the device idle
+// for.  Both kernels do the same arithmetic in the same order: their results are the same bits.
+template <typename T>
+__global__ void __launch_bounds__(kFinishWarps * 32)
+qkv_finish_heads_kernel(const float* __restrict__ sums, int ld, const float* __restrict__ bias,
+                  const float2* __restrict__ cos_sin, int rot, int unit_norm, float eps,
+                  const float* __restrict__ v_first, float* __restrict__ v_keep, float lambda,
+                  T* __restrict__ q_out, int ldq, float* __restrict__ gate_out,
+                  T* __restrict__ kc, T* __restrict__ vc, long long page_stride,
+                  const int* __restrict__ block_table, int table_stride,
+                  const int* __restrict__ token_seq, const int* __restrict__ slots,
+                  const int* __restrict__ positions,
+                  int n_heads, int n_kv, int hd, int vd, int has_gate) {
+    chain_release();
+    chain_wait();
+    extern __shared__ __align__(16) float staged[];          // [warp][hd]: the head a warp is turning
+    const int n = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_w = n_heads * hd, k_w = n_kv * hd, v_w = n_kv * vd;
+    const int n_turning = n_heads + n_kv;
+    const int n_items = n_turning + n_kv + (has_gate ? 1 : 0);
+    const float* src = sums + (size_t)n * ld;
+    const int pos = positions[n];
+    size_t page_off = 0;
+    bool page_known = false;
+    for (int item = blockIdx.y * kFinishWarps + warp; item < n_items; item += gridDim.y * kFinishWarps) {
+        if (kc && !page_known && item >= n_heads && item < n_turning + n_kv) {
+            const int slot = slots[token_seq[n]];
+            page_off = (size_t)block_table[(size_t)slot * table_stride + pos / kPageTokens] * page_stride;
+            page_known = true;
+        }
+        if (item < n_turning) {
+            // a query or key head: bias, rotation, unit norm, store
+            float* x = staged + (size_t)warp * hd;
+            const int at = item * hd;
+            for (int i = lane; i < hd; i += 32) x[i] = src[at + i] + (bias ? __ldg(bias + at + i) : 0.f);
+            __syncwarp();
+            const int rhalf = rot >> 1;
+            if (cos_sin) {
+                for (int i = lane; i < rhalf; i += 32) {
+                    const float2 cs = cos_sin[(size_t)n * rhalf + i];
+                    const float a = x[i], b = x[i + rhalf];
+                    x[i] = a * cs.x - b * cs.y;
+                    x[i + rhalf] = b * cs.x + a * cs.y;
+                }
+                __syncwarp();
+            }
+            float inv = 1.f;
+            if (unit_norm) {
+                float sq = 0.f;
+                for (int i = lane; i < hd; i += 32) sq = fmaf(x[i], x[i], sq);
+                inv = 1.0f / sqrtf(warp_sum(sq) / (float)hd + eps);
+            }
+            T* dst;
+            if (item < n_heads) dst = q_out + (size_t)n * ldq + (size_t)item * hd;
+            else if (kc) dst = kc + page_off + ((size_t)(item - n_heads) * kPageTokens + (pos % kPageTokens)) * hd;
+            else { __syncwarp(); continue; }
+            if (hd % 2 == 0 && (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(T))) == 0) {
+                for (int i = lane * 2; i < hd; i += 64) store_pair(dst + i, x[i] * inv, x[i + 1] * inv);
+            } else {
+                for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(x[i] * inv);
+            }
+            __syncwarp();                                        // before the warp's next head overwrites x
+            continue;
+        }
+        if (item < n_turning + n_kv) {
+            // a value head: bias, kept for later layers, blended, store
+            const int head = item - n_turning;
+            const int at = q_w + k_w + head * vd;
+            const size_t step_at = (size_t)n * v_w + (size_t)head * vd;
+            T* dst = vc ? vc + page_off + ((size_t)head * kPageTokens + (pos % kPageTokens)) * vd : nullptr;
+            for (int c = lane; c < vd; c += 32) {
+                float val = src[at + c] + (bias ? __ldg(bias + at + c) : 0.f);
+                if (v_keep) v_keep[step_at + c] = val;
+                if (v_first) val = (1.0f - lambda) * val + lambda * v_first[step_at + c];
+                if (dst) dst[c] = from_f32<T>(val);
+            }
+            continue;
+        }
+        // the gates: one sigmoid a query head, no bias
+        for (int h = lane; h < n_heads; h += 32)
+            gate_out[(size_t)n * n_heads + h] = 1.0f / (1.0f + expf(-src[q_w + k_w + v_w + h]));
+    }
+}
 }  // namespace
 
 GTG_API int gtg_qkv_finish(int dtype, const float* sums, int ld, const float* bias, const float* cos_sin, int rot,
@@ -140,16 +231,22 @@ GTG_API int gtg_qkv_finish(int dtype, const float* sums, int ld, const float* bi
     const int has_gate = gate_out != nullptr;
     const int width = n_heads * hd + n_kv * (hd + vd) + (has_gate ? n_heads : 0);
     if (ld < width) return kErrBadArgument;
-    const size_t smem = (size_t)width * sizeof(float);
+    // up to kFewTokens tokens a warp per head over several blocks a token, beyond a block per token
+    constexpr int kFewTokens = 512;
+    const bool few = N <= kFewTokens;
+    const size_t smem = few ? (size_t)kFinishWarps * hd * sizeof(float) : (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return kErrUnsupported;
+    const int n_items = n_heads + 2 * n_kv + has_gate;
+    const dim3 grid(N, few ? (n_items + kFinishWarps - 1) / kFinishWarps : 1);
+    if (grid.y > 65535) return kErrUnsupported;
 #define GTG_FINISH(T)                                                                                              \
     do {                                                                                                           \
-        auto kernel = qkv_finish_kernel<T>;                                                                        \
+        auto kernel = few ? qkv_finish_heads_kernel<T> : qkv_finish_rows_kernel<T>;                                \
         if (smem > 48 * 1024) {                                                                                    \
             const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                                   \
         }                                                                                                          \
-        return launch_chained(kernel, dim3(N), dim3(256), smem, stream, sums, ld, bias, (const float2*)cos_sin, rot, \
+        return launch_chained(kernel, grid, dim3(kFinishWarps * 32), smem, stream, sums, ld, bias, (const float2*)cos_sin, rot, \
                               unit_norm, eps, v_first, v_keep, lambda, (T*)q_out, ldq, gate_out, (T*)kc, (T*)vc,    \
                               page_stride, block_table, table_stride, token_seq, slots, positions, n_heads, n_kv,  \
                               hd, vd, has_gate);                                                                   \

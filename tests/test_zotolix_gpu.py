@@ -175,7 +175,7 @@ def test_copies_of_the_hidden_state_are_made_updated_read_and_normed(dtype, S, H
     assert torch.equal(before, copies)
 
 
-def _finish(dtype, n_heads, n_kv, hd, vd, rot, base, starts, lens, *, unit, gate, blend, seed=0):
+def _finish(dtype, n_heads, n_kv, hd, vd, rot, base, starts, lens, *, unit, gate, blend, seed=0, chunk=50):
     """Float sums of a projection through `qkv_finish` into a cache, the rows cut into one sequence per
     (start, length); returns what the plain pieces say and what the kernel left."""
     rng = np.random.default_rng(seed)
@@ -185,7 +185,8 @@ def _finish(dtype, n_heads, n_kv, hd, vd, rot, base, starts, lens, *, unit, gate
     bias = rng.standard_normal(width - (n_heads if gate else 0))
     v_first = rng.standard_normal((n, n_kv * vd))
     rt = Runtime(DEV, TORCH[dtype])
-    cache = Cache([[KVRequest(n_kv, hd, None, value_dim=vd, chunk=50)]], [None], max_tokens=64 * 8, max_slots=len(lens) + 1,
+    cache = Cache([[KVRequest(n_kv, hd, None, value_dim=vd, chunk=chunk)]], [None],
+                  max_tokens=max(64 * 8, 64 * sum((a + l + 63) // 64 for a, l in zip(starts, lens))), max_slots=len(lens) + 1,
                   dtype=TORCH[dtype], device=DEV)
     cache.open_sequence()                                       # slot 0 stays unused: slots and batch places differ
     slots = [cache.open_sequence() for _ in lens]
@@ -235,6 +236,9 @@ def test_projection_sums_are_biased_rotated_normed_blended_gated_and_stored(dtyp
     _finish(dtype, 6, 3, 10, 5, 10, 50.0, [126, 0, 63], [3, 1, 2], unit=False, gate=True, blend=None, seed=1)
     _finish(dtype, 2, 1, 128, 64, 64, 1e6, [200], [1], unit=True, gate=True, blend=1.0, seed=2)
     _finish(dtype, 1, 1, 6, 7, 0, 1.0, [5], [4], unit=False, gate=False, blend=0.0, seed=3)
+    # many tokens take the kernel with a block a token, few the one with a warp a head: the same numbers from both
+    _finish(dtype, 5, 1, 24, 16, 12, 300.0, [0, 3], [530, 70], unit=True, gate=True, blend=0.25, seed=4, chunk=None)
+    _finish(dtype, 3, 3, 9, 5, 4, 30.0, [7], [520], unit=False, gate=False, blend=None, seed=5, chunk=None)
 
 
 def _filled_cache(dtype, n_kv, hd, vd, lengths, rng, chunk=None, window=None):
