@@ -100,6 +100,18 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
         }
     };
 
+    // A 16-row fragment none of whose rows exists (the padding of an expert's last tile; nearly all of a tile in a
+    // decode step) is neither read nor multiplied: its sums would not be written.  Warp-uniform.
+    bool live[MI];
+    bool any_live = false;
+#pragma unroll
+    for (int i = 0; i < MI; ++i) {
+        live[i] = false;
+        const int r0 = wm * (BM / 2) + i * 16;
+        for (int r = 0; r < 16; ++r) live[i] = live[i] || src[r0 + r] >= 0;
+        any_live = any_live || live[i];
+    }
+
     float acc[MI][4][4];
 #pragma unroll
     for (int i = 0; i < MI; ++i)
@@ -125,9 +137,11 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
         const uint32_t w_base = a_base + BM * BK * 2;
 #pragma unroll
         for (int kk = 0; kk < BK / 16; ++kk) {
+            if (!any_live) break;
             uint32_t af[MI][4];
 #pragma unroll
             for (int i = 0; i < MI; ++i) {
+                if (!live[i]) continue;
                 const int r = wm * (BM / 2) + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
                 const int c = kk * 2 + (lane >> 4);
                 ldmatrix_x4(af[i][0], af[i][1], af[i][2], af[i][3], a_base + swz_offset<BK>(r, c));
@@ -141,9 +155,11 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
                             w_base + swz_offset<BK>(r, c));
             }
 #pragma unroll
-            for (int i = 0; i < MI; ++i)
+            for (int i = 0; i < MI; ++i) {
+                if (!live[i]) continue;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) mma_bf16_16816(acc[i][j], af[i], bfr[j][0], bfr[j][1]);
+            }
         }
     }
     cp_async_wait<0>();
