@@ -151,6 +151,9 @@ attention_masked_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
 #pragma unroll
     for (int r = 0; r < 2; ++r) row_lo[r] = first_seen(row_pos[r], window, chunk);
 
+    // a warp none of whose sixteen rows exists (three of four in a decode step of four heads a group) stages
+    // pages with the others and computes nothing
+    const bool warp_live = warp * 16 < rows_here;
     for (int j = j_lo, it = 0; j <= j_hi; ++j, ++it) {
         const int stage = it & 1;
         if (j + 1 <= j_hi) {
@@ -161,91 +164,93 @@ attention_masked_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
             cp_async_wait<0>();
         }
         __syncthreads();
-        if (it == 0) {
+        if (warp_live) {
+            if (it == 0) {
+#pragma unroll
+                for (int kk = 0; kk < DKP / 16; ++kk) {
+                    const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    const int c = kk * 2 + (lane >> 4);
+                    ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], sQ + swz_offset<DKP>(r, c));
+                }
+            }
+            // ---- S = Q K^T for this warp's 16 rows and the page's 64 keys
+            float s[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+            const uint32_t kbase = sK + stage * KTILE, vbase = sV + stage * VTILE;
 #pragma unroll
             for (int kk = 0; kk < DKP / 16; ++kk) {
-                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                const int c = kk * 2 + (lane >> 4);
-                ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], sQ + swz_offset<DKP>(r, c));
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    uint32_t b0, b1, b2, b3;
+                    const int r = jj * 16 + (lane & 7) + (lane >> 4) * 8;
+                    const int c = kk * 2 + ((lane >> 3) & 1);
+                    ldmatrix_x4(b0, b1, b2, b3, kbase + swz_offset<DKP>(r, c));
+                    mma_bf16_16816(s[jj * 2], qf[kk], b0, b1);
+                    mma_bf16_16816(s[jj * 2 + 1], qf[kk], b2, b3);
+                }
             }
-        }
-        // ---- S = Q K^T for this warp's 16 rows and the page's 64 keys
-        float s[8][4];
+            // ---- mask by position (only pages that cross an edge for some row of this warp)
+            const bool all_visible = (j * kPageTokens + kPageTokens - 1 <= warp_pos_lo) && (j * kPageTokens >= warp_seen_hi);
+            if (!all_visible) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-        const uint32_t kbase = sK + stage * KTILE, vbase = sV + stage * VTILE;
+                for (int i = 0; i < 8; ++i) {
 #pragma unroll
-        for (int kk = 0; kk < DKP / 16; ++kk) {
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                uint32_t b0, b1, b2, b3;
-                const int r = jj * 16 + (lane & 7) + (lane >> 4) * 8;
-                const int c = kk * 2 + ((lane >> 3) & 1);
-                ldmatrix_x4(b0, b1, b2, b3, kbase + swz_offset<DKP>(r, c));
-                mma_bf16_16816(s[jj * 2], qf[kk], b0, b1);
-                mma_bf16_16816(s[jj * 2 + 1], qf[kk], b2, b3);
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = j * kPageTokens + i * 8 + t4 * 2 + (e & 1);
+                        const int r = e >> 1;
+                        if (key > row_pos[r] || key < row_lo[r]) s[i][e] = -INFINITY;
+                    }
+                }
             }
-        }
-        // ---- mask by position (only pages that cross an edge for some row of this warp)
-        const bool all_visible = (j * kPageTokens + kPageTokens - 1 <= warp_pos_lo) && (j * kPageTokens >= warp_seen_hi);
-        if (!all_visible) {
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[i][e]);
+            }
+            float corr[2], m_use[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_row[r], mx[r] * sl2);          // scale > 0: max commutes with it
+                m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+                corr[r] = fast_exp2(m_row[r] - m_use[r]);
+                m_row[r] = m_new;
+                l_row[r] *= corr[r];
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int key = j * kPageTokens + i * 8 + t4 * 2 + (e & 1);
-                    const int r = e >> 1;
-                    if (key > row_pos[r] || key < row_lo[r]) s[i][e] = -INFINITY;
+                    const float p = fast_exp2(fmaf(s[i][e], sl2, -m_use[e >> 1]));
+                    s[i][e] = p;
+                    l_row[e >> 1] += p;
                 }
             }
-        }
-        float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[i][e]);
-        }
-        float corr[2], m_use[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_row[r], mx[r] * sl2);          // scale > 0: max commutes with it
-            m_use[r] = m_new == -INFINITY ? 0.f : m_new;
-            corr[r] = fast_exp2(m_row[r] - m_use[r]);
-            m_row[r] = m_new;
-            l_row[r] *= corr[r];
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float p = fast_exp2(fmaf(s[i][e], sl2, -m_use[e >> 1]));
-                s[i][e] = p;
-                l_row[e >> 1] += p;
+            for (int i = 0; i < DVP / 8; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
             }
-        }
+            // ---- O += P V
 #pragma unroll
-        for (int i = 0; i < DVP / 8; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0];
-            o[i][2] *= corr[1]; o[i][3] *= corr[1];
-        }
-        // ---- O += P V
+            for (int kk = 0; kk < 4; ++kk) {
+                uint32_t pa[4];
+                pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-            uint32_t pa[4];
-            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-            for (int dd = 0; dd < DVP / 16; ++dd) {
-                uint32_t b0, b1, b2, b3;
-                const int r = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-                const int c = dd * 2 + (lane >> 4);
-                ldmatrix_x4_trans(b0, b1, b2, b3, vbase + swz_offset<DVP>(r, c));
-                mma_bf16_16816(o[dd * 2], pa, b0, b1);
-                mma_bf16_16816(o[dd * 2 + 1], pa, b2, b3);
+                for (int dd = 0; dd < DVP / 16; ++dd) {
+                    uint32_t b0, b1, b2, b3;
+                    const int r = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                    const int c = dd * 2 + (lane >> 4);
+                    ldmatrix_x4_trans(b0, b1, b2, b3, vbase + swz_offset<DVP>(r, c));
+                    mma_bf16_16816(o[dd * 2], pa, b0, b1);
+                    mma_bf16_16816(o[dd * 2 + 1], pa, b2, b3);
+                }
             }
         }
         __syncthreads();
