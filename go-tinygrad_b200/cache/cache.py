@@ -142,8 +142,9 @@ class _KVGroup:
 
 
 class Cache:
-    """`requests[i]` lists what schedule entry i needs (empty for an entry that
-    reads another entry's storage: then `shared_from[i]` names that entry)."""
+    """`requests[i]` lists what schedule entry i needs; `shared_from[i]` names the
+    entry whose key/value storage entry i reads instead of having its own (such
+    an entry asks for no keys and values, but may ask for fixed-size state)."""
 
     def __init__(self, requests: Sequence[Sequence[Request]], shared_from: Sequence[Optional[int]],
                  *, max_tokens: int, max_slots: Optional[int] = None, max_position: Optional[int] = None,
@@ -212,7 +213,10 @@ class Cache:
             if owner in kv_of_entry:
                 g, j = kv_of_entry[owner]
                 kv = self.groups[g].view(j)
-            self.handles.append(CacheHandle(kv, states_of_entry.get(owner, {}), writes=src is None))
+            # an entry that reads another entry's keys and values may still keep state of its own
+            states = dict(states_of_entry.get(owner, {}))
+            states.update(states_of_entry.get(i, {}))
+            self.handles.append(CacheHandle(kv, states, writes=src is None))
 
     # ------------------------------------------------------------ sequences
     def open_sequence(self) -> int:

@@ -218,6 +218,106 @@ qkv_finish_heads_kernel(const float* __restrict__ sums, int ld, const float* __r
             gate_out[(size_t)n * n_heads + h] = 1.0f / (1.0f + expf(-src[q_w + k_w + v_w + h]));
     }
 }
+// ---- projections that pass a short convolution over time -------------------------------
+// For mixers whose q, k and v pass, channel by channel, a causal convolution over
+// the last `taps` tokens before anything else happens to them.  Of a token's float
+// sums out of the projection,  [ q: n_heads x hd | k: n_kv x hd | v: n_kv x vd ]
+// (n_kv = 0: the layer has queries only and reads another layer's keys and values),
+// a warp takes one head and, all in float,
+//   * adds the bias and convolves: y_t[c] = sum_j w[j, c] u_(t - taps + 1 + j)[c], u the
+//     biased sums; tokens of this step are read from the sums, earlier ones from
+//     conv_state[slot] ([taps-1, C], the sequence's last raw sums, oldest first), and
+//     what lies before the sequence's first token is zero.  The taps are added oldest
+//     first, whatever the cut of the sequence into steps;
+//   * norms every query and key head, x / sqrt(mean(x^2) + eps) * w (weights of hd
+//     channels, shared by the heads; null: no norm);
+//   * rotates the first `rot` channels of every query and key head by the token's
+//     (cos, sin) table: channel 2i with 2i+1 (`interleaved`) or i with i + rot/2;
+// then rounds once: queries to q_out, keys and values into the token's cache place.
+// The state is left as it was: `conv_state_update` over the same sums follows.
+template <typename T>
+__global__ void __launch_bounds__(kFinishWarps * 32)
+qkv_conv_finish_kernel(const float* __restrict__ sums, int ld, const float* __restrict__ bias,
+                       const float* __restrict__ conv_w, int taps, const float* __restrict__ conv_state,
+                       const int* __restrict__ cu_seqlens,
+                       const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                       const float2* __restrict__ cos_sin, int rot, int interleaved,
+                       T* __restrict__ q_out, int ldq, T* __restrict__ kc, T* __restrict__ vc, long long page_stride,
+                       const int* __restrict__ block_table, int table_stride,
+                       const int* __restrict__ token_seq, const int* __restrict__ slots,
+                       const int* __restrict__ positions, int n_heads, int n_kv, int hd, int vd) {
+    chain_release();
+    chain_wait();
+    extern __shared__ __align__(16) float staged[];          // [warp][hd]: the head a warp is working on
+    const int n = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_w = n_heads * hd, k_w = n_kv * hd;
+    const int C = q_w + k_w + n_kv * vd;
+    const int n_turning = n_heads + n_kv, n_items = n_turning + n_kv;
+    const int b = token_seq[n];
+    const int before = n - cu_seqlens[b];                    // rows of this sequence before n in the step
+    const int pos = positions[n];
+    const int keep = taps - 1;
+    const float* st = keep > 0 ? conv_state + (size_t)slots[b] * keep * C : nullptr;
+    auto convolved = [&](int c) -> float {
+        const float bc = bias ? __ldg(bias + c) : 0.f;
+        if (keep <= 0) return sums[(size_t)n * ld + c] + bc;
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = keep - j;
+            if (pos - back < 0) continue;                    // before the sequence's first token: nothing
+            const float u = before - back >= 0 ? sums[(size_t)(n - back) * ld + c] : st[(size_t)(keep + before - back) * C + c];
+            acc = fmaf(__ldg(conv_w + (size_t)j * C + c), u + bc, acc);
+        }
+        return acc;
+    };
+    size_t page_off = 0;
+    if (kc) page_off = (size_t)block_table[(size_t)slots[b] * table_stride + pos / kPageTokens] * page_stride;
+    const int rhalf = rot >> 1;
+    for (int item = blockIdx.y * kFinishWarps + warp; item < n_items; item += gridDim.y * kFinishWarps) {
+        if (item >= n_turning) {
+            // a value head: convolved and stored
+            const int head = item - n_turning;
+            if (!vc) continue;
+            T* dst = vc + page_off + ((size_t)head * kPageTokens + (pos % kPageTokens)) * vd;
+            for (int c = lane; c < vd; c += 32) dst[c] = from_f32<T>(convolved(q_w + k_w + head * vd + c));
+            continue;
+        }
+        const bool is_q = item < n_heads;
+        if (!is_q && !kc) continue;
+        float* x = staged + (size_t)warp * hd;
+        float sq = 0.f;
+        for (int i = lane; i < hd; i += 32) {
+            const float v = convolved(item * hd + i);
+            x[i] = v;
+            sq = fmaf(v, v, sq);
+        }
+        const float* w = is_q ? q_norm : k_norm;
+        if (w) {
+            const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)hd + eps);
+            for (int i = lane; i < hd; i += 32) x[i] = x[i] * inv * __ldg(w + i);
+        }
+        __syncwarp();
+        if (cos_sin) {
+            for (int i = lane; i < rhalf; i += 32) {
+                const float2 cs = cos_sin[(size_t)n * rhalf + i];
+                const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + rhalf;
+                const float a = x[ia], bb = x[ib];
+                x[ia] = a * cs.x - bb * cs.y;
+                x[ib] = bb * cs.x + a * cs.y;
+            }
+            __syncwarp();
+        }
+        T* dst = is_q ? q_out + (size_t)n * ldq + (size_t)item * hd
+                      : kc + page_off + ((size_t)(item - n_heads) * kPageTokens + (pos % kPageTokens)) * hd;
+        if (hd % 2 == 0 && (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(T))) == 0) {
+            for (int i = lane * 2; i < hd; i += 64) store_pair(dst + i, x[i], x[i + 1]);
+        } else {
+            for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(x[i]);
+        }
+        __syncwarp();                                        // before the warp's next head overwrites x
+    }
+}
 }  // namespace
 
 GTG_API int gtg_qkv_finish(int dtype, const float* sums, int ld, const float* bias, const float* cos_sin, int rot,
@@ -254,5 +354,40 @@ GTG_API int gtg_qkv_finish(int dtype, const float* sums, int ld, const float* bi
     if (dtype == 0) GTG_FINISH(float);
     if (dtype == 1) GTG_FINISH(bf16);
 #undef GTG_FINISH
+    return kErrBadArgument;
+}
+
+GTG_API int gtg_qkv_conv_finish(int dtype, const float* sums, int ld, const float* bias, const float* conv_w, int taps,
+                                const float* conv_state, const int* cu_seqlens, const float* q_norm, const float* k_norm,
+                                float eps, const float* cos_sin, int rot, int interleaved, void* q_out, int ldq,
+                                void* kc, void* vc, long long page_stride, const int* block_table, int table_stride,
+                                const int* token_seq, const int* slots, const int* positions, int N, int n_heads,
+                                int n_kv, int hd, int vd, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (n_heads <= 0 || n_kv < 0 || hd <= 0 || vd <= 0 || rot < 0 || (rot & 1) || rot > hd || taps < 1) return kErrBadArgument;
+    if ((cos_sin != nullptr) != (rot > 0) || (kc == nullptr) != (vc == nullptr)) return kErrBadArgument;
+    if (taps > 1 && (!conv_w || !conv_state)) return kErrBadArgument;
+    if (n_kv == 0 && kc) return kErrBadArgument;
+    if (ld < n_heads * hd + n_kv * (hd + vd)) return kErrBadArgument;
+    const size_t smem = (size_t)kFinishWarps * hd * sizeof(float);
+    if (smem > 200 * 1024) return kErrUnsupported;
+    const int n_items = n_heads + 2 * n_kv;
+    const dim3 grid(N, (n_items + kFinishWarps - 1) / kFinishWarps);
+    if (grid.y > 65535) return kErrUnsupported;
+#define GTG_CONV_FINISH(T)                                                                                         \
+    do {                                                                                                           \
+        auto kernel = qkv_conv_finish_kernel<T>;                                                                   \
+        if (smem > 48 * 1024) {                                                                                    \
+            const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                                   \
+        }                                                                                                          \
+        return launch_chained(kernel, grid, dim3(kFinishWarps * 32), smem, stream, sums, ld, bias, conv_w, taps,   \
+                              conv_state, cu_seqlens, q_norm, k_norm, eps, (const float2*)cos_sin, rot, interleaved, \
+                              (T*)q_out, ldq, (T*)kc, (T*)vc, page_stride, block_table, table_stride, token_seq,   \
+                              slots, positions, n_heads, n_kv, hd, vd);                                            \
+    } while (0)
+    if (dtype == 0) GTG_CONV_FINISH(float);
+    if (dtype == 1) GTG_CONV_FINISH(bf16);
+#undef GTG_CONV_FINISH
     return kErrBadArgument;
 }

@@ -19,7 +19,11 @@
 // the output then has vd channels per head.  `vrow` is the width of a row of the
 // value plane (hd when keys and values share a page layout; a cache whose values
 // have a size of their own stores rows of vd channels).  `gate` (or null):
-// float [N, n_heads], a factor on each head's output.
+// float [N, n_heads], a factor on each head's output; with `gate_ld` > 0 it holds
+// instead one logit per output channel, rows of gate_ld floats, heads side by side
+// vd apart, and the factor is the logit's sigmoid.  `softcap` c > 0: a score
+// becomes c tanh(score / c) after the scale.  `sinks` (or null): float [n_heads];
+// exp(sinks[h]) joins head h's softmax denominator, without a key or a value.
 #include "common.cuh"
 #include <math.h>
 
@@ -36,7 +40,7 @@ attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
                         const int* __restrict__ token_seq, const int* __restrict__ slots,
                         const int* __restrict__ positions,
                         int N, int n_heads, int n_kv, int hd, int vd, int vrow, float scale, int window, int chunk,
-                        const float* __restrict__ gate) {
+                        const float* __restrict__ gate, int gate_ld, float softcap, const float* __restrict__ sinks) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * kWarps + warp;
@@ -69,6 +73,7 @@ attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
             float s = 0.f;
             for (int d = 0; d < hd; ++d) s = fmaf(qs[d], to_f32<T>(kp[d]), s);
             score = s * scale;
+            if (softcap > 0.f) score = softcap * tanhf(score / softcap);
         }
         const float m_new = fmaxf(m, warp_max(score));
         const float p = valid ? expf(score - m_new) : 0.f;
@@ -90,11 +95,24 @@ attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
         }
         m = m_new;
     }
-    const float inv = (gate ? gate[(size_t)n * n_heads + h] : 1.0f) / l;
+    if (sinks) {
+        // the sink joins the sum as one more weight that carries no value
+        const float sink = sinks[h];
+        const float m_new = fmaxf(m, sink);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sink - m_new);
+#pragma unroll
+        for (int j = 0; j < kMaxPerLane; ++j) acc[j] *= corr;
+    }
+    const float inv = ((gate && gate_ld <= 0) ? gate[(size_t)n * n_heads + h] : 1.0f) / l;
 #pragma unroll
     for (int j = 0; j < kMaxPerLane; ++j) {
         const int d = lane + 32 * j;
-        if (d < vd) out[(size_t)n * ldo + h * vd + d] = from_f32<T>(acc[j] * inv);
+        if (d < vd) {
+            float val = acc[j] * inv;
+            if (gate && gate_ld > 0) val *= 1.0f / (1.0f + expf(-gate[(size_t)n * gate_ld + h * vd + d]));
+            out[(size_t)n * ldo + h * vd + d] = from_f32<T>(val);
+        }
     }
 }
 }  // namespace
@@ -104,10 +122,11 @@ GTG_API int gtg_attention_simple(int dtype, const void* q, int ldq, void* out, i
                                  const int* block_table, int table_stride,
                                  const int* token_seq, const int* slots, const int* positions,
                                  int N, int n_heads, int n_kv, int hd, int vd, int vrow, float scale, int window, int chunk,
-                                 const float* gate, cudaStream_t stream) {
+                                 const float* gate, int gate_ld, float softcap, const float* sinks, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || hd <= 0) return kErrBadArgument;
-    if (vd <= 0 || vd > vrow || window < 0 || chunk < 0) return kErrBadArgument;
+    if (vd <= 0 || vd > vrow || window < 0 || chunk < 0 || softcap < 0.f) return kErrBadArgument;
+    if (gate && gate_ld > 0 && gate_ld < n_heads * vd) return kErrBadArgument;
     if (hd > kMaxHeadDim || vd > 32 * 32) return kErrUnsupported;
     const long long warps = (long long)N * n_heads;
     const long long blocks = (warps + kWarps - 1) / kWarps;
@@ -116,7 +135,7 @@ GTG_API int gtg_attention_simple(int dtype, const void* q, int ldq, void* out, i
 #define GTG_SIMPLE(T, PER)                                                                                   \
     attention_simple_kernel<T, PER><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(                            \
         (const T*)q, ldq, (T*)out, ldo, (const T*)kc, (const T*)vc, page_stride, block_table, table_stride,      \
-        token_seq, slots, positions, N, n_heads, n_kv, hd, vd, vrow, scale, window, chunk, gate)
+        token_seq, slots, positions, N, n_heads, n_kv, hd, vd, vrow, scale, window, chunk, gate, gate_ld, softcap, sinks)
     if (dtype == 0) {
         if (vd <= 256) GTG_SIMPLE(float, 8); else if (vd <= 512) GTG_SIMPLE(float, 16); else GTG_SIMPLE(float, 32);
     } else if (dtype == 1) {

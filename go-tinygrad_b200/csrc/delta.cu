@@ -1,0 +1,241 @@
+// Kernels of the gated delta rule: a recurrent mixer whose per-sequence state is,
+// per head, a matrix S of d x dv floats (key channels by value channels) that is
+// decayed row by row and corrected towards the new value along the new key:
+//
+//     S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
+//
+// with one decay g_t[i] in (0, 1) per head and key channel, a step beta_t in (0, 1)
+// per head, and q_t, k_t of a key/value group (several heads may share them).
+//
+// All of them serve a step of packed rows: sequence b owns rows
+// cu_seqlens[b]..cu_seqlens[b+1], continues from the state kept for its cache slot
+// and leaves the state for its next step; a prompt, a portion of one and a single
+// token are the same case.  Everything here is float whatever the activation type:
+// unit norms, decays with their softplus and exponentials, steps, the state and the
+// sums of the recurrence, and the norm of the read-out.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+// log(1 + exp(x)) without overflow and without a cut-off
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+// ------------------------------------------------------------- per-token preparation
+// One block per token.  In place, on float rows:
+//   * every query and key head (n_groups of each, d channels, side by side from qk):
+//     x / sqrt(sum(x^2) + unit_eps); queries also times q_scale;
+//   * decay[n, h, i] <- exp(-exp(a_log[h]) * softplus(decay[n, h, i] + dt_bias[h, i]));
+//   * beta[n, h] <- sigmoid(beta_in[n, h]).
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(float* __restrict__ qk, int ld_qk, float* __restrict__ decay, int ld_decay,
+                     const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                     const float* __restrict__ beta_in, int ld_beta_in, float* __restrict__ beta,
+                     int n_heads, int n_groups, int d, float unit_eps, float q_scale) {
+    chain_release();
+    chain_wait();
+    const size_t n = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int item = warp; item < 2 * n_groups; item += n_warps) {
+        float* x = qk + n * ld_qk + (size_t)item * d;
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) ss = fmaf(x[i], x[i], ss);
+        const float inv = (item < n_groups ? q_scale : 1.0f) / sqrtf(warp_sum(ss) + unit_eps);
+        for (int i = lane; i < d; i += 32) x[i] *= inv;
+    }
+    float* g = decay + n * ld_decay;
+    for (int c = threadIdx.x; c < n_heads * d; c += blockDim.x) {
+        const float rate = expf(a_log[c / d]);
+        g[c] = expf(-rate * softplus_f(g[c] + dt_bias[c]));
+    }
+    for (int h = threadIdx.x; h < n_heads; h += blockDim.x)
+        beta[n * n_heads + h] = 1.0f / (1.0f + expf(-beta_in[n * ld_beta_in + h]));
+}
+
+// ------------------------------------------------------------ the recurrence
+// The columns of S never meet: column j is a recurrence of its own over d numbers,
+//     r1 = sum_i g_i S_ij k_i,  r2 = sum_i g_i S_ij q_i,  u_j = beta (v_j - r1),
+//     S_ij <- g_i S_ij + k_i u_j,  o_j = r2 + u_j (k . q)
+// (o = S^T q over the new S, written out so that both sums run over the old one and
+// meet in one exchange).  One block serves (head, a slice of kColsPerBlock columns,
+// sequence).  R threads share a column: thread (r, j) owns rows r, r + R, ... (up to
+// kRows of them); their partial sums meet by shuffles.  q, k, g, v and beta of a tile
+// of tokens at a time are staged in shared memory.  Tokens are walked strictly in
+// order: the result does not depend on the cut of the sequence into steps, on the
+// batch or on the slices.
+constexpr int kRows = 16;          // rows of S a thread owns at most
+constexpr int kScanThreads = 128;
+constexpr int kTile = 16;          // tokens staged at a time
+
+__global__ void __launch_bounds__(kScanThreads)
+delta_scan_kernel(const float* __restrict__ qk, int ld_qk, const float* __restrict__ v, int ld_v,
+                  const float* __restrict__ decay, int ld_decay, const float* __restrict__ beta,
+                  float* __restrict__ state, float* __restrict__ out, int ld_out,
+                  const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                  int n_heads, int n_groups, int d, int dv, int R, int slices) {
+    chain_release();
+    chain_wait();
+    extern __shared__ float smem[];
+    const int cols = kScanThreads / R;                       // columns a block serves
+    float* sq = smem;                                        // [kTile][d]
+    float* sk = sq + kTile * d;
+    float* sg = sk + kTile * d;
+    float* sv = sg + kTile * d;                              // [kTile][cols]
+    float* sb = sv + kTile * cols;                           // [kTile] beta, then [kTile] k . q
+    const int h = blockIdx.x / slices, slice = blockIdx.x % slices;
+    const int b = blockIdx.y;
+    const int grp = h / (n_heads / n_groups);
+    const int row0 = cu_seqlens[b], n_rows = cu_seqlens[b + 1] - row0;
+    const int tid = threadIdx.x;
+    const int cw = 32 / R;                                   // columns a warp serves: the R lanes of a column lie cw apart
+    const int jj = (tid >> 5) * cw + (tid & 31) % cw, r = (tid & 31) / cw;
+    const int j = slice * cols + jj;
+    const bool col_ok = j < dv;
+    float* S = state + ((size_t)slots[b] * n_heads + h) * (size_t)d * dv;
+    float s[kRows];
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+        const int row = r + i * R;
+        s[i] = (col_ok && row < d) ? S[(size_t)row * dv + j] : 0.f;
+    }
+    for (int t0 = 0; t0 < n_rows; t0 += kTile) {
+        const int nt = min(kTile, n_rows - t0);
+        __syncthreads();                                     // the tile before has been used up
+        for (int idx = tid; idx < nt * d; idx += kScanThreads) {
+            const int t = idx / d, i = idx - t * d;
+            const size_t row = (size_t)(row0 + t0 + t);
+            sq[t * d + i] = qk[row * ld_qk + (size_t)grp * d + i];
+            sk[t * d + i] = qk[row * ld_qk + (size_t)(n_groups + grp) * d + i];
+            sg[t * d + i] = decay[row * ld_decay + (size_t)h * d + i];
+        }
+        for (int idx = tid; idx < nt * cols; idx += kScanThreads) {
+            const int t = idx / cols, c = idx - t * cols;
+            const int col = slice * cols + c;
+            sv[t * cols + c] = col < dv ? v[(size_t)(row0 + t0 + t) * ld_v + (size_t)h * dv + col] : 0.f;
+        }
+        if (tid < nt) sb[tid] = beta[(size_t)(row0 + t0 + tid) * n_heads + h];
+        __syncthreads();
+        // k . q of every token of the tile: a warp a token at a time, in a fixed order
+        for (int t = tid >> 5; t < nt; t += kScanThreads / 32) {
+            float kq = 0.f;
+            for (int i = tid & 31; i < d; i += 32) kq = fmaf(sk[t * d + i], sq[t * d + i], kq);
+            kq = warp_sum(kq);
+            if ((tid & 31) == 0) sb[kTile + t] = kq;
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float* kt = sk + t * d;
+            const float* qt = sq + t * d;
+            const float* gt = sg + t * d;
+            float r1 = 0.f, r2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < kRows; ++i) {
+                const int row = r + i * R;
+                if (row < d) {
+                    s[i] *= gt[row];
+                    r1 = fmaf(s[i], kt[row], r1);
+                    r2 = fmaf(s[i], qt[row], r2);
+                }
+            }
+            for (int o = cw; o < 32; o <<= 1) {
+                r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+                r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+            }
+            const float u = sb[t] * (sv[t * cols + jj] - r1);
+#pragma unroll
+            for (int i = 0; i < kRows; ++i) {
+                const int row = r + i * R;
+                if (row < d) s[i] = fmaf(kt[row], u, s[i]);
+            }
+            if (r == 0 && col_ok)
+                out[(size_t)(row0 + t0 + t) * ld_out + (size_t)h * dv + j] = fmaf(u, sb[kTile + t], r2);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+        const int row = r + i * R;
+        if (col_ok && row < d) S[(size_t)row * dv + j] = s[i];
+    }
+}
+
+// ---------------------------------------------- norm per head, weight, sigmoid gate
+// out[n, h, c] = y[n, h, c] / sqrt(mean_c(y[n, h, :]^2) + eps) * weight[c] * sigmoid(gate[n, h, c]):
+// every head of the read-out by its own root mean square, a weight of dv channels that
+// the heads share, and a gate from float logits.  A warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_norm_gate_kernel(const float* __restrict__ y, int ld_y, const float* __restrict__ gate, int ld_gate,
+                      const float* __restrict__ weight, float eps, T* __restrict__ out, int ld_out,
+                      long long n_items, int n_heads, int dv) {
+    chain_release();
+    chain_wait();
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= n_items) return;
+    const int lane = threadIdx.x & 31;
+    const size_t n = (size_t)(item / n_heads);
+    const int h = (int)(item % n_heads);
+    const float* src = y + n * ld_y + (size_t)h * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(src[c], src[c], ss);
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+    const float* gt = gate + n * ld_gate + (size_t)h * dv;
+    T* dst = out + n * ld_out + (size_t)h * dv;
+    for (int c = lane; c < dv; c += 32)
+        dst[c] = from_f32<T>(src[c] * inv * weight[c] * (1.0f / (1.0f + expf(-gt[c]))));
+}
+}  // namespace
+
+GTG_API int gtg_delta_prepare(float* qk, int ld_qk, float* decay, int ld_decay, const float* dt_bias, const float* a_log,
+                              const float* beta_in, int ld_beta_in, float* beta, int N, int n_heads, int n_groups, int d,
+                              float unit_eps, float q_scale, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (n_heads <= 0 || n_groups <= 0 || n_heads % n_groups || d <= 0) return kErrBadArgument;
+    if (ld_qk < 2 * n_groups * d || ld_decay < n_heads * d || ld_beta_in < n_heads) return kErrBadArgument;
+    return launch_chained(delta_prepare_kernel, dim3(N), dim3(256), 0, stream, qk, ld_qk, decay, ld_decay, dt_bias, a_log,
+                          beta_in, ld_beta_in, beta, n_heads, n_groups, d, unit_eps, q_scale);
+}
+
+// How many threads share a column of the state: the least power of two that leaves a
+// thread at most kRows rows.
+static int delta_split(int d) {
+    int R = 1;
+    while (R < 32 && (d + R - 1) / R > kRows) R *= 2;
+    return R;
+}
+
+GTG_API int gtg_delta_scan_supports(int d, int dv) {
+    return d > 0 && dv > 0 && d <= 32 * kRows && (size_t)(3 * kTile * d + kTile * kScanThreads + 2 * kTile) * 4 <= 200 * 1024;
+}
+
+GTG_API int gtg_delta_scan(const float* qk, int ld_qk, const float* v, int ld_v, const float* decay, int ld_decay,
+                           const float* beta, float* state, float* out, int ld_out, const int* cu_seqlens,
+                           const int* slots, int n_seqs, int n_heads, int n_groups, int d, int dv, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (n_heads <= 0 || n_groups <= 0 || n_heads % n_groups) return kErrBadArgument;
+    if (!gtg_delta_scan_supports(d, dv)) return kErrUnsupported;
+    if (ld_qk < 2 * n_groups * d || ld_v < n_heads * dv || ld_decay < n_heads * d || ld_out < n_heads * dv) return kErrBadArgument;
+    if (n_seqs > 65535) return kErrUnsupported;
+    const int R = delta_split(d);
+    const int cols = kScanThreads / R;
+    const int slices = (dv + cols - 1) / cols;
+    const size_t smem = (size_t)(3 * kTile * d + kTile * cols + 2 * kTile) * sizeof(float);
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return launch_chained(delta_scan_kernel, dim3(n_heads * slices, n_seqs), dim3(kScanThreads), smem, stream, qk, ld_qk, v, ld_v,
+                          decay, ld_decay, beta, state, out, ld_out, cu_seqlens, slots, n_heads, n_groups, d, dv, R, slices);
+}
+
+GTG_API int gtg_head_norm_gate(int dtype, const float* y, int ld_y, const float* gate, int ld_gate, const float* weight,
+                               float eps, void* out, int ld_out, int N, int n_heads, int dv, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (n_heads <= 0 || dv <= 0 || ld_y < n_heads * dv || ld_gate < n_heads * dv || ld_out < n_heads * dv) return kErrBadArgument;
+    const long long items = (long long)N * n_heads;
+    const long long blocks = (items + 7) / 8;
+    if (blocks > 0x7fffffffLL) return kErrUnsupported;
+    if (dtype == 0) return launch_chained(head_norm_gate_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, y, ld_y, gate,
+                                          ld_gate, weight, eps, (float*)out, ld_out, items, n_heads, dv);
+    if (dtype == 1) return launch_chained(head_norm_gate_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, stream, y, ld_y, gate,
+                                          ld_gate, weight, eps, (bf16*)out, ld_out, items, n_heads, dv);
+    return kErrBadArgument;
+}

@@ -155,10 +155,11 @@ GTG_API int gtg_add_rmsnorm(int dtype, float* residual, const void* pending, con
 }
 
 // ------------------------------------------------------------------ SwiGLU
-// out[m,i] = silu(gu[m,i]) * gu[m,I+i],  silu(g) = g / (1 + exp(-g))
-// (backends/simd/vec.go:52-59).  `gu` holds the gate columns then the up columns.
+// out[m,i] = act(gu[m,i]) * gu[m,I+i]; act is silu, g / (1 + exp(-g))
+// (backends/simd/vec.go:52-59), or another of the pointwise activations (`kind`).
+// `gu` holds the gate columns then the up columns.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I, int kind) {
     chain_release();
     chain_wait();
     const size_t total = (size_t)M * I;
@@ -168,19 +169,20 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         const int i = (int)(idx - m * I);
         const float g = to_f32<T>(gu[m * 2 * I + i]);
         const float u = to_f32<T>(gu[m * 2 * I + I + i]);
-        const float s = g / (1.0f + expf(-g));
+        const float s = kind == 2 ? g / (1.0f + expf(-g)) : activate(g, kind);
         out[idx] = from_f32<T>(s * u);
     }
 }
 
-GTG_API int gtg_swiglu(int dtype, const void* gu, void* out, int M, int I, cudaStream_t stream) {
+GTG_API int gtg_swiglu(int dtype, const void* gu, void* out, int M, int I, int kind, cudaStream_t stream) {
     int st = 0;
     if (M <= 0 || I <= 0) return 0;
+    if (kind < 0 || kind >= kActivations) return kErrBadArgument;
     const size_t total = (size_t)M * I;
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
-    if (dtype == 0) st = launch_chained(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, M, I);
-    else if (dtype == 1) st = launch_chained(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, M, I);
+    if (dtype == 0) st = launch_chained(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, M, I, kind);
+    else if (dtype == 1) st = launch_chained(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, M, I, kind);
     else return kErrBadArgument;
     return st;
 }
@@ -874,4 +876,40 @@ GTG_API int gtg_sigmoid_gate(int dtype, void* x, int ldx, const void* g, int ldg
     if (dtype == 0) return launch_chained(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, ldx, (const float*)g, ldg, M, N);
     if (dtype == 1) return launch_chained(sigmoid_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ldx, (const bf16*)g, ldg, M, N);
     return kErrBadArgument;
+}
+
+// ---- a norm of the float hidden state in place, a factor on float rows -------------
+// x[n,:] <- x[n,:] / sqrt(mean(x[n,:]^2) + eps) * w, float throughout: the norm that
+// stands directly behind the token embedding and changes the hidden state itself.
+__global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ w, float eps, int H) {
+    chain_release();
+    chain_wait();
+    __shared__ float scratch[33];
+    float* row = x + (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+    const float total = block_sum(ss, scratch);
+    const float s = 1.0f / sqrtf(total / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = row[i] * s * w[i];
+}
+
+GTG_API int gtg_rmsnorm_rows(float* x, const float* w, float eps, int N, int H, cudaStream_t stream) {
+    if (N <= 0 || H <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : H >= 256 ? 128 : 64;
+    return launch_chained(rmsnorm_rows_kernel, dim3(N), dim3(threads), 0, stream, x, w, eps, H);
+}
+
+__global__ void scale_kernel(float* __restrict__ x, size_t total, float factor) {
+    chain_release();
+    chain_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+        x[idx] *= factor;
+}
+
+// x <- factor * x, float (a multiplier on the logits).
+GTG_API int gtg_scale(float* x, long long total, float factor, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    return launch_chained(scale_kernel, dim3(blocks), dim3(256), 0, stream, x, (size_t)total, factor);
 }

@@ -18,8 +18,8 @@
 //     (the head of the row is written by the product with U_h^T), or, without
 //     such rows (q_full null), in place.
 // rows_out, if given, receives the token's cache row once more, token by token.
-// Rotation: of the part's first `rdims` channels, (2i, 2i+1) turn by the angle of pair i, whose cosine and
-// sine (amplitude included) come from the step's table [token, rot/2].
+// Rotation: of the part's first `rdims` channels, (2i, 2i+1) (`interleaved`) or (i, i + rdims/2) turn by the
+// angle of pair i, whose cosine and sine (amplitude included) come from the step's table [token, rdims/2].
 #include "mma_helpers.cuh"
 #include <math.h>
 
@@ -31,12 +31,14 @@ latent_prepare_kernel(T* __restrict__ q, int ldq, const T* __restrict__ dkv, int
                       T* __restrict__ kc, long long page_stride, const int* __restrict__ block_table,
                       int table_stride, const int* __restrict__ token_seq, const int* __restrict__ slots,
                       const int* __restrict__ positions, T* __restrict__ q_full, int ldf,
-                      int n_heads, int dim, int rot, int rdims, int rank, T* __restrict__ rows_out, int ldo) {
+                      int n_heads, int dim, int rot, int rdims, int rank, T* __restrict__ rows_out, int ldo,
+                      int interleaved) {
     chain_release();
     chain_wait();
     __shared__ float scratch[33];
     const int n = blockIdx.x;
     const int half = rdims / 2;   // pairs that turn; channels rdims..rot-1 of the part pass unchanged
+    const int pa = interleaved ? 2 : 1, pb = interleaved ? 1 : half;     // pair i is channels (pa * i, pa * i + pb)
     const float2* cs = cos_sin + (size_t)n * half;
     if (dkv) {
         const T* d = dkv + (size_t)n * ldd;
@@ -57,11 +59,12 @@ latent_prepare_kernel(T* __restrict__ q, int ldq, const T* __restrict__ dkv, int
             if (copy) copy[i] = row[i];
         }
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const float u = to_f32<T>(d[rank + 2 * i]), v = to_f32<T>(d[rank + 2 * i + 1]);
+            const int ia = pa * i, ib = ia + pb;
+            const float u = to_f32<T>(d[rank + ia]), v = to_f32<T>(d[rank + ib]);
             const float2 a = cs[i];
-            row[rank + 2 * i] = from_f32<T>(u * a.x - v * a.y);
-            row[rank + 2 * i + 1] = from_f32<T>(v * a.x + u * a.y);
-            if (copy) { copy[rank + 2 * i] = row[rank + 2 * i]; copy[rank + 2 * i + 1] = row[rank + 2 * i + 1]; }
+            row[rank + ia] = from_f32<T>(u * a.x - v * a.y);
+            row[rank + ib] = from_f32<T>(v * a.x + u * a.y);
+            if (copy) { copy[rank + ia] = row[rank + ia]; copy[rank + ib] = row[rank + ib]; }
         }
         for (int i = rdims + threadIdx.x; i < rot; i += blockDim.x) {
             row[rank + i] = d[rank + i];
@@ -73,10 +76,11 @@ latent_prepare_kernel(T* __restrict__ q, int ldq, const T* __restrict__ dkv, int
         for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
             const int h = idx / half, i = idx % half;
             T* p = q + (size_t)n * ldq + (size_t)h * (dim + rot) + dim;
-            const float u = to_f32<T>(p[2 * i]), v = to_f32<T>(p[2 * i + 1]);
+            const int ia = pa * i, ib = ia + pb;
+            const float u = to_f32<T>(p[ia]), v = to_f32<T>(p[ib]);
             const float2 a = cs[i];
-            p[2 * i] = from_f32<T>(u * a.x - v * a.y);
-            p[2 * i + 1] = from_f32<T>(v * a.x + u * a.y);
+            p[ia] = from_f32<T>(u * a.x - v * a.y);
+            p[ib] = from_f32<T>(v * a.x + u * a.y);
         }
         return;
     }
@@ -84,11 +88,12 @@ latent_prepare_kernel(T* __restrict__ q, int ldq, const T* __restrict__ dkv, int
     for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
         const int h = idx / half, i = idx % half;
         const T* src = q + (size_t)n * ldq + (size_t)h * (dim + rot) + dim;
-        const float u = to_f32<T>(src[2 * i]), v = to_f32<T>(src[2 * i + 1]);
+        const int ia = pa * i, ib = ia + pb;
+        const float u = to_f32<T>(src[ia]), v = to_f32<T>(src[ib]);
         const float2 a = cs[i];
         T* dst = q_full + (size_t)n * ldf + (size_t)h * D + rank;
-        dst[2 * i] = from_f32<T>(u * a.x - v * a.y);
-        dst[2 * i + 1] = from_f32<T>(v * a.x + u * a.y);
+        dst[ia] = from_f32<T>(u * a.x - v * a.y);
+        dst[ib] = from_f32<T>(v * a.x + u * a.y);
     }
     for (int idx = threadIdx.x; idx < n_heads * (rot - rdims); idx += blockDim.x) {
         const int h = idx / (rot - rdims), i = rdims + idx % (rot - rdims);
@@ -101,7 +106,7 @@ GTG_API int gtg_latent_prepare(int dtype, void* q, int ldq, const void* dkv, int
                                const float* norm_w, float eps, void* kc, long long page_stride,
                                const int* block_table, int table_stride, const int* token_seq, const int* slots,
                                const int* positions, void* q_full, int ldf, int N, int n_heads, int dim, int rot,
-                               int rdims, int rank, void* rows_out, int ldo, cudaStream_t stream) {
+                               int rdims, int rank, void* rows_out, int ldo, int interleaved, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (n_heads <= 0 || dim <= 0 || rot <= 0 || rdims < 0 || rdims > rot || rdims % 2 || rank <= 0) return kErrBadArgument;
     if (dkv && (!kc || !norm_w || !block_table)) return kErrBadArgument;
@@ -109,12 +114,12 @@ GTG_API int gtg_latent_prepare(int dtype, void* q, int ldq, const void* dkv, int
         return launch_chained(latent_prepare_kernel<float>, dim3(N), dim3(128), 0, stream, (float*)q, ldq,
                               (const float*)dkv, ldd, (const float2*)cos_sin, norm_w, eps, (float*)kc, page_stride,
                               block_table, table_stride, token_seq, slots, positions, (float*)q_full, ldf, n_heads,
-                              dim, rot, rdims, rank, (float*)rows_out, ldo);
+                              dim, rot, rdims, rank, (float*)rows_out, ldo, interleaved);
     if (dtype == 1)
         return launch_chained(latent_prepare_kernel<bf16>, dim3(N), dim3(128), 0, stream, (bf16*)q, ldq,
                               (const bf16*)dkv, ldd, (const float2*)cos_sin, norm_w, eps, (bf16*)kc, page_stride,
                               block_table, table_stride, token_seq, slots, positions, (bf16*)q_full, ldf, n_heads,
-                              dim, rot, rdims, rank, (bf16*)rows_out, ldo);
+                              dim, rot, rdims, rank, (bf16*)rows_out, ldo, interleaved);
     return kErrBadArgument;
 }
 
@@ -189,7 +194,10 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
                             const bf16* __restrict__ kc, long long page_stride, const int* __restrict__ block_table,
                             int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                             const int* __restrict__ start_pos, int n_heads, int D, int rank, float scale, int window,
-                            int n_splits, float* __restrict__ scratch, int total_rows, int test_waits) {
+                            int n_splits, float* __restrict__ scratch, int total_rows, int test_waits,
+                            const float* __restrict__ sinks) {
+    // sinks (or null): float [n_heads]; exp(sinks[h]) joins head h's softmax denominator without a key or a value
+    // (with several runs of keys the merge kernel adds it).
     // test_waits (the test hook's form of the launch): no page is ever copied and a wait polls a thousand
     // times, so that every wait runs out, the status word is set and the block still returns
     chain_release();
@@ -421,7 +429,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
     for (int hh = 0; hh < 2; ++hh) {
         const int row = r0 + rg * 16 + g + hh * 8;
         if (pos_r[hh] < 0 || l_run[hh] <= 0.f) continue;
-        const float inv = 1.0f / l_run[hh];
+        const float inv = 1.0f / (l_run[hh] + (sinks ? exp2f(sinks[row % n_heads] * kLog2e - m_run[hh]) : 0.f));
         bf16* dst = out + (size_t)(tok0 + row / n_heads) * ldo + (size_t)(row % n_heads) * rank + tile_lo * 8 + t * 2;
 #pragma unroll
         for (int j = 0; j < NT; ++j)
@@ -434,7 +442,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
 // keys brought together, z in order.
 __global__ void __launch_bounds__(128)
 latent_attention_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out, int ldo, int n_heads, int rank,
-                              int n_splits, int total_rows) {
+                              int n_splits, int total_rows, const float* __restrict__ sinks) {
     chain_release();
     chain_wait();
     __shared__ float ms[64], ls[64], ws[64];
@@ -453,6 +461,7 @@ latent_attention_merge_kernel(const float* __restrict__ scratch, bf16* __restric
     __syncthreads();
     float L = 0.f;
     for (int z = 0; z < n_splits; ++z) L = fmaf(ws[z], ls[z], L);
+    if (sinks) L += exp2f(sinks[row % n_heads] * kLog2e - M);
     const float inv = 1.0f / L;
     bf16* dst = out + (size_t)(row / n_heads) * ldo + (size_t)(row % n_heads) * rank;
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
@@ -522,7 +531,7 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
                                       const int* block_table, int table_stride, const int* cu_seqlens, const int* slots,
                                       const int* start_pos, int n_seqs, int max_q_len, int n_heads, int D, int rank,
                                       float scale, int window, int n_splits, float* scratch, int n_tokens,
-                                      cudaStream_t stream) {
+                                      const float* sinks, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (n_heads <= 0) return kErrBadArgument;
     if (!gtg_latent_attention_supports(D, rank)) return kErrUnsupported;
@@ -545,7 +554,7 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
         st = launch_chained(latent_attention_mma_kernel<NT>, grid, dim3(kLatThreads), smem, stream, (const bf16*)q, ldq, \
                             (bf16*)out, ldo, (const bf16*)kc, page_stride, block_table, table_stride, cu_seqlens, slots, \
                             start_pos, n_heads, D, rank, scale, window, n_splits, scratch, total_rows,              \
-                            g_latent_test_waits ? 1 : 0);                                                          \
+                            g_latent_test_waits ? 1 : 0, sinks);                                                   \
     } while (0)
     const int per = ((rank / 8) + kParts - 1) / kParts;
     int st = 0;
@@ -553,7 +562,7 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
 #undef GTG_LATENT
     if (st != 0 || n_splits == 1) return st;
     return launch_chained(latent_attention_merge_kernel, dim3(total_rows), dim3(128), 0, stream, (const float*)scratch,
-                          (bf16*)out, ldo, n_heads, rank, n_splits, total_rows);
+                          (bf16*)out, ldo, n_heads, rank, n_splits, total_rows, sinks);
 }
 
 // ---- prompts that start their sequences: keys and values expanded per head ---------------
@@ -579,7 +588,8 @@ template <int KS, int NV>
 __global__ void __launch_bounds__(kExpThreads)
 expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kv, int ldkv,
                           bf16* __restrict__ out, int ldo, const int* __restrict__ cu_seqlens,
-                          int dim, int rot, int vdim, float scale, int window, int test_waits) {
+                          int dim, int rot, int vdim, float scale, int window, int test_waits,
+                          const float* __restrict__ sinks) {
     chain_release();
     chain_wait();
     extern __shared__ __align__(128) unsigned char smem[];
@@ -754,7 +764,7 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         if (pos_r[hh] < 0 || l_run[hh] <= 0.f) continue;
-        const float inv = 1.0f / l_run[hh];
+        const float inv = 1.0f / (l_run[hh] + (sinks ? exp2f(sinks[h] * kLog2e - m_run[hh]) : 0.f));
         bf16* dst = out + (size_t)(tok0 + pos_r[hh]) * ldo + (size_t)h * vdim + t * 2;
 #pragma unroll
         for (int j = 0; j < NV; ++j)
@@ -800,7 +810,7 @@ GTG_API int gtg_latent_spread(const void* kr, int ldr, void* kv, int ldkv, int N
 GTG_API int gtg_expanded_attention_bf16(const void* q, int ldq, const void* kv, int ldkv,
                                         void* out, int ldo, const int* cu_seqlens, int n_seqs,
                                         int max_q_len, int n_heads, int dim, int rot, int vdim, float scale, int window,
-                                        cudaStream_t stream) {
+                                        const float* sinks, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (n_heads <= 0) return kErrBadArgument;
     if (!gtg_expanded_attention_supports(dim, rot, vdim)) return kErrUnsupported;
@@ -819,7 +829,7 @@ GTG_API int gtg_expanded_attention_bf16(const void* q, int ldq, const void* kv, 
         }                                                                                                           \
         return launch_chained(expanded_attention_kernel<KS, NV>, grid, dim3(kExpThreads), smem, stream, (const bf16*)q, ldq, \
                               (const bf16*)kv, ldkv, (bf16*)out, ldo, cu_seqlens,                                  \
-                              dim, rot, vdim, scale, window, g_latent_test_waits ? 1 : 0);                         \
+                              dim, rot, vdim, scale, window, g_latent_test_waits ? 1 : 0, sinks);                  \
     } while (0)
     const int ks = (dim + rot) / 16;
     if (vdim <= 64) {

@@ -13,7 +13,7 @@ from typing import Any, List, Mapping, Optional, Sequence, Union
 
 import torch
 
-from ..cache import Cache
+from ..cache import Cache, StateRequest
 from ..config.registry import Architecture, find_architecture, read_config_json
 from ..parts.base import Block, Runtime, build_part, walk
 from ..parts.plan import ModelPlan, plan_weight_specs
@@ -121,7 +121,8 @@ class Model:
                 requests.append(list(self.blocks[entry.layer].cache_requests()))
                 shared.append(None)
             else:
-                requests.append([])
+                # it reads another run's keys and values; state of fixed size is its own
+                requests.append([r for r in self.blocks[entry.layer].cache_requests() if isinstance(r, StateRequest)])
                 shared.append(entry.cache)
         return Cache(requests, shared, max_tokens=max_tokens, max_slots=max_slots,
                      max_position=self.plan.max_position, dtype=self.rt.dtype, device=self.rt.device)

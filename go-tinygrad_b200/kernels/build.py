@@ -46,6 +46,7 @@ LIBRARIES: Dict[str, str] = {
     "hyper": "hyper.cu",
     "attention_prep": "attention_prep.cu",
     "attention_masked": "attention_masked.cu",
+    "delta": "delta.cu",
 }
 # sources a library's file includes textually (they count for staleness)
 INCLUDED_SOURCES: Dict[str, List[str]] = {"attention_decode_static.cu": ["attention_bf16.cu"]}

@@ -23,7 +23,9 @@ _P, _I, _L, _F, _U, _D = c_void_p, c_int, c_longlong, c_float, c_ulonglong, c_do
 _SIGNATURES = {
     "gtg_embed": ("elementwise", [_I, _P, _P, _P, _I, _I, _I, _F, _P]),
     "gtg_add_rmsnorm": ("elementwise", [_I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
-    "gtg_swiglu": ("elementwise", [_I, _P, _P, _I, _I, _P]),
+    "gtg_swiglu": ("elementwise", [_I, _P, _P, _I, _I, _I, _P]),
+    "gtg_rmsnorm_rows": ("elementwise", [_P, _P, _F, _I, _I, _P]),
+    "gtg_scale": ("elementwise", [_P, _L, _F, _P]),
     "gtg_rope_table": ("elementwise", [_P, _P, _P, _I, _I, _D, _P]),
     "gtg_rope_kv_store": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P]),
     "gtg_add_layernorm": ("elementwise", [_I, _P, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
@@ -55,7 +57,13 @@ _SIGNATURES = {
     "gtg_gemm_bf16_swapab_scratch_floats": ("gemm_bf16_swapab", [_I, _I, _I]),
     "gtg_gemm_bf16_swapab_status": ("gemm_bf16_swapab", []),
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
-                                                  _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P]),
+                                                  _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I, _F, _P, _P]),
+    "gtg_qkv_conv_finish": ("attention_prep", [_I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _F, _P, _I, _I, _P, _I, _P, _P, _L, _P, _I,
+                                               _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_delta_prepare": ("delta", [_P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P]),
+    "gtg_delta_scan_supports": ("delta", [_I, _I]),
+    "gtg_delta_scan": ("delta", [_P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_head_norm_gate": ("delta", [_I, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _I, _P]),
     "gtg_rmsnorm_add": ("elementwise", [_I, _I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
     "gtg_round_rows": ("elementwise", [_I, _P, _P, _L, _P]),
     "gtg_swiglu_bias": ("elementwise", [_I, _P, _P, _P, _P, _I, _I, _I, _P]),
@@ -65,14 +73,14 @@ _SIGNATURES = {
     "gtg_gemm_bf16_grouped": ("gemm_bf16_grouped", [_P, _I, _L, _P, _I, _P, _I, _L, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I,
                                                     _I, _P, _I, _L, _P]),
     "gtg_latent_prepare": ("latent", [_I, _P, _I, _P, _I, _P, _P, _F, _P, _L, _P, _I, _P, _P, _P, _P, _I,
-                                      _I, _I, _I, _I, _I, _I, _P, _I, _P]),
+                                      _I, _I, _I, _I, _I, _I, _P, _I, _I, _P]),
     "gtg_expanded_attention_supports": ("latent", [_I, _I, _I]),
-    "gtg_expanded_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]),
+    "gtg_expanded_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P]),
     "gtg_latent_spread": ("latent", [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_latent_attention_supports": ("latent", [_I, _I]),
     "gtg_latent_status": ("latent", []),
     "gtg_latent_test_hooks": ("latent", [_I]),
-    "gtg_latent_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I, _P]),
+    "gtg_latent_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I, _P, _P]),
     "gtg_latent_attention_splits": ("latent", [_I, _I, _I, _I, _I, _I]),
     "gtg_moe_gather": ("experts", [_P, _I, _P, _I, _P, _I, _I, _P]),
     "gtg_gemm_bf16_tcgen05_grouped": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
@@ -297,13 +305,14 @@ def add_rmsnorm(residual: torch.Tensor, pending: Optional[torch.Tensor], weight:
                                   _ptr(out), _ptr(rows), R, H, _stream()), "add_rmsnorm")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[m,i] = act(gate_up[m,i]) * gate_up[m,I+i], act = silu or another of `ACTIVATIONS`."""
+    _need(activation in ACTIVATIONS, f"swiglu: activation {activation!r} is not known; known: {sorted(ACTIVATIONS)}")
     M, two_i = gate_up.shape
     _need(two_i % 2 == 0 and gate_up.is_contiguous() and out.is_contiguous()
           and tuple(out.shape) == (M, two_i // 2) and out.dtype == gate_up.dtype,
           "swiglu: gate_up [M, 2I] and out [M, I] must be contiguous and of one dtype")
-    _check(_fn("gtg_swiglu")(_dt(out), _ptr(gate_up), _ptr(out), M, two_i // 2, _stream()), "swiglu")
+    _check(_fn("gtg_swiglu")(_dt(out), _ptr(gate_up), _ptr(out), M, two_i // 2, ACTIVATIONS[activation], _stream()), "swiglu")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor, amplitude: float = 1.0) -> None:
@@ -391,6 +400,7 @@ def add_layernorm(residual: torch.Tensor, pending: Optional[torch.Tensor], weigh
 
 
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+GATED_EPILOGUES = {"silu": "swiglu"}     # gate activations whose product act(gate) * up the products' epilogues form
 EPILOGUE_ACTIVATION = 16      # a product's epilogue code from here on: the plain product, then activation (code - 16)
 
 
@@ -407,6 +417,21 @@ def softcap(logits: torch.Tensor, cap: float) -> None:
     _need(logits.dtype == torch.float32 and logits.is_contiguous(), "softcap: logits must be contiguous float32")
     _need(cap > 0, "softcap: the cap must be positive")
     _check(_fn("gtg_softcap")(_ptr(logits), logits.numel(), float(cap), _stream()), "softcap")
+
+
+def scale(x: torch.Tensor, factor: float) -> None:
+    """x <- factor * x in place (float32): a multiplier on the logits."""
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "scale: x must be contiguous float32")
+    _check(_fn("gtg_scale")(_ptr(x), x.numel(), float(factor), _stream()), "scale")
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """x[n] <- x[n] / sqrt(mean(x[n]^2) + eps) * weight, in place on float32 rows: a norm
+    that changes the hidden state itself (the one directly behind the token embedding)."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "rmsnorm_rows: x must be contiguous float32 [N, H]")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == x.shape[1],
+          "rmsnorm_rows: weight must be float32 [H]")
+    _check(_fn("gtg_rmsnorm_rows")(_ptr(x), _ptr(weight), float(eps), x.shape[0], x.shape[1], _stream()), "rmsnorm_rows")
 
 
 def hidden_concat(residual: torch.Tensor, pending: Optional[torch.Tensor], other: torch.Tensor,
@@ -555,6 +580,131 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
     _need(x.shape == gate.shape and x.dtype == gate.dtype, "sigmoid_gate: x and gate must agree in shape and dtype")
     _check(_fn("gtg_sigmoid_gate")(_dt(x), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0), x.shape[0], x.shape[1],
                                    _stream()), "sigmoid_gate")
+
+
+def qkv_conv_finish(sums: torch.Tensor, bias: Optional[torch.Tensor], conv_w: Optional[torch.Tensor],
+                    conv_state: Optional[torch.Tensor], cu_seqlens, q_norm: Optional[torch.Tensor],
+                    k_norm: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor], interleaved: bool,
+                    n_heads: int, n_kv: int, head_dim: int, value_dim: int, kv, q_out: torch.Tensor,
+                    token_seq, slots, positions, store: bool = True) -> None:
+    """Between the fused projection and the attention, for mixers whose q, k and v pass a
+    short causal convolution over time: of the float32 sums [N, >= q | k | v] (n_kv key and
+    value heads; 0: queries only) add the bias [q | k | v], convolve every channel over the
+    last taps tokens (conv_w float32 [taps, C], oldest tap first; earlier steps' raw sums from
+    conv_state float32 [slots, taps-1, C]; None: no convolution), norm every query and key
+    head with q_norm / k_norm (float32 [head_dim]; None: no norm), rotate the head's first
+    2 * cos_sin.shape[1] channels (2i with 2i+1 if `interleaved`, else i with i + half),
+    write queries to q_out and, with `store`, keys and values to the cache.  The state is
+    not changed: `conv_state_update` over the same sums follows."""
+    _rows2d(sums, "qkv_conv_finish: sums"); _rows2d(q_out, "qkv_conv_finish: q_out")
+    N = sums.shape[0]
+    C = n_heads * head_dim + n_kv * (head_dim + value_dim)
+    _need(sums.dtype == torch.float32 and sums.shape[1] >= C, "qkv_conv_finish: sums must be float32 rows of q | k | v")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C),
+          "qkv_conv_finish: bias must be float32 [q | k | v]")
+    taps = 1
+    if conv_w is not None:
+        taps = conv_w.shape[0]
+        _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and tuple(conv_w.shape) == (taps, C),
+              "qkv_conv_finish: conv_w must be float32 [taps, q | k | v]")
+        _need(taps == 1 or (conv_state is not None and conv_state.dtype == torch.float32 and conv_state.is_contiguous()
+                            and tuple(conv_state.shape[1:]) == (taps - 1, C)),
+              "qkv_conv_finish: conv_state must be float32 [slots, taps-1, q | k | v]")
+    for name, t in (("q_norm", q_norm), ("k_norm", k_norm)):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == head_dim),
+              f"qkv_conv_finish: {name} must be float32 [head_dim]")
+    rot = 0
+    if cos_sin is not None:
+        _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.dim() == 3 and cos_sin.shape[0] == N
+              and cos_sin.shape[2] == 2, "qkv_conv_finish: cos_sin must be float32 [N, pairs, 2]")
+        rot = 2 * cos_sin.shape[1]
+        _need(rot <= head_dim, "qkv_conv_finish: more rotated channels than a head has")
+    _need(q_out.shape[0] == N and q_out.shape[1] >= n_heads * head_dim, "qkv_conv_finish: q_out is too narrow")
+    store = bool(store and n_kv > 0)
+    if store:
+        _need(kv.k.dtype == q_out.dtype and kv.n_kv_heads == n_kv and kv.head_dim == head_dim and kv.value_dim == value_dim,
+              "qkv_conv_finish: the cache entry does not match the heads")
+    _int32("qkv_conv_finish", cu_seqlens, token_seq, slots, positions)
+    if store:
+        _check_access("qkv_conv_finish", 0, kv, slots, positions, token_seq, n_items=N)
+    _check(_fn("gtg_qkv_conv_finish")(_dt(q_out), _ptr(sums), sums.stride(0), _ptr(bias), _ptr(conv_w), taps, _ptr(conv_state),
+                                      _ptr(cu_seqlens), _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos_sin), rot,
+                                      1 if interleaved else 0, _ptr(q_out), q_out.stride(0),
+                                      _ptr(kv.k) if store else None, _ptr(kv.v) if store else None,
+                                      kv.page_stride if store else 0, _ptr(kv.block_table) if store else None,
+                                      kv.table_stride if store else 0, _ptr(token_seq), _ptr(slots), _ptr(positions),
+                                      N, n_heads, n_kv, head_dim, value_dim, _stream()), "qkv_conv_finish")
+
+
+# ------------------------------------------------------------- the gated delta rule
+DELTA_MAX_KEY_DIM = 512       # most key channels a head of the delta rule's state may have (16 rows a lane, 32 lanes)
+
+
+def delta_scan_supports(key_dim: int, value_dim: int) -> bool:
+    return bool(_fn("gtg_delta_scan_supports")(int(key_dim), int(value_dim)))
+
+
+def delta_prepare(qk: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                  beta_in: torch.Tensor, beta: torch.Tensor, n_heads: int, n_groups: int, key_dim: int,
+                  unit_eps: float, q_scale: float) -> None:
+    """Per token, in place on float32 rows: every query and key head of qk ([N, >= 2 * n_groups *
+    key_dim], queries then keys) becomes x / sqrt(sum(x^2) + unit_eps), queries also times
+    q_scale; decay [N, n_heads * key_dim] becomes exp(-exp(a_log[h]) softplus(decay + dt_bias));
+    beta [N, n_heads] = sigmoid(beta_in [N, n_heads])."""
+    _rows2d(qk, "delta_prepare: qk"); _rows2d(decay, "delta_prepare: decay"); _rows2d(beta_in, "delta_prepare: beta_in")
+    N = qk.shape[0]
+    _need(qk.dtype == decay.dtype == beta_in.dtype == beta.dtype == torch.float32, "delta_prepare: float32 rows only")
+    _need(qk.shape[1] >= 2 * n_groups * key_dim and tuple(decay.shape) == (N, n_heads * key_dim)
+          and tuple(beta_in.shape) == (N, n_heads) and tuple(beta.shape) == (N, n_heads) and beta.is_contiguous(),
+          "delta_prepare: qk [N, 2 groups * d], decay [N, heads * d], beta_in and beta [N, heads]")
+    _need(dt_bias.dtype == torch.float32 and dt_bias.is_contiguous() and dt_bias.numel() == n_heads * key_dim
+          and a_log.dtype == torch.float32 and a_log.is_contiguous() and a_log.numel() == n_heads,
+          "delta_prepare: dt_bias float32 [heads * d], a_log float32 [heads]")
+    _check(_fn("gtg_delta_prepare")(_ptr(qk), qk.stride(0), _ptr(decay), decay.stride(0), _ptr(dt_bias), _ptr(a_log),
+                                    _ptr(beta_in), beta_in.stride(0), _ptr(beta), N, n_heads, n_groups, key_dim,
+                                    float(unit_eps), float(q_scale), _stream()), "delta_prepare")
+
+
+def delta_scan(qk: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+               out: torch.Tensor, cu_seqlens, slots, n_seqs: int, n_heads: int, n_groups: int, key_dim: int,
+               value_dim: int) -> None:
+    """The gated delta rule, token by token, all float32: per head h (queries and keys of
+    group h // (n_heads / n_groups)), S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T;
+    out = S^T q.  qk [N, >= 2 groups * d] (queries, then keys), v [N, heads * dv], decay
+    [N, heads * d], beta [N, heads]; state [slots, heads, d, dv], read and left per
+    sequence; out [N, heads * dv]."""
+    for name, t in (("qk", qk), ("v", v), ("decay", decay), ("out", out)):
+        _rows2d(t, f"delta_scan: {name}")
+        _need(t.dtype == torch.float32, f"delta_scan: {name} must be float32")
+    N = qk.shape[0]
+    _need(qk.shape[1] >= 2 * n_groups * key_dim and tuple(v.shape) == (N, n_heads * value_dim)
+          and tuple(decay.shape) == (N, n_heads * key_dim) and tuple(out.shape) == (N, n_heads * value_dim),
+          "delta_scan: qk [N, 2 groups * d], v and out [N, heads * dv], decay [N, heads * d]")
+    _need(beta.dtype == torch.float32 and beta.is_contiguous() and tuple(beta.shape) == (N, n_heads),
+          "delta_scan: beta must be contiguous float32 [N, heads]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (n_heads, key_dim, value_dim),
+          "delta_scan: state must be float32 [slots, heads, d, dv]")
+    _need(delta_scan_supports(key_dim, value_dim), f"delta_scan: a state of {key_dim} x {value_dim} a head is not supported")
+    _int32("delta_scan", cu_seqlens, slots)
+    _check(_fn("gtg_delta_scan")(_ptr(qk), qk.stride(0), _ptr(v), v.stride(0), _ptr(decay), decay.stride(0), _ptr(beta),
+                                 _ptr(state), _ptr(out), out.stride(0), _ptr(cu_seqlens), _ptr(slots), int(n_seqs),
+                                 n_heads, n_groups, key_dim, value_dim, _stream()), "delta_scan")
+
+
+def head_norm_gate(y: torch.Tensor, gate_logits: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                   n_heads: int) -> None:
+    """out[n, h, :] = y[n, h, :] / sqrt(mean(y[n, h, :]^2) + eps) * weight * sigmoid(gate_logits[n, h, :]):
+    y and gate_logits float32 [N, heads * dv], weight float32 [dv] shared by the heads."""
+    _rows2d(y, "head_norm_gate: y"); _rows2d(gate_logits, "head_norm_gate: gate"); _rows2d(out, "head_norm_gate: out")
+    N, width = y.shape
+    _need(width % n_heads == 0, "head_norm_gate: the row is not a whole number of heads")
+    dv = width // n_heads
+    _need(y.dtype == torch.float32 and gate_logits.dtype == torch.float32 and tuple(gate_logits.shape) == (N, width)
+          and tuple(out.shape) == (N, width), "head_norm_gate: y and gate float32 [N, heads * dv], out of that shape")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == dv,
+          "head_norm_gate: weight must be float32 [dv]")
+    _check(_fn("gtg_head_norm_gate")(_dt(out), _ptr(y), y.stride(0), _ptr(gate_logits), gate_logits.stride(0), _ptr(weight),
+                                     float(eps), _ptr(out), out.stride(0), N, n_heads, dv, _stream()), "head_norm_gate")
 
 
 # ------------------------------------------------------------- recurrent mixers
@@ -888,12 +1038,16 @@ def attention_bf16_supports(head_dim: int) -> bool:
 
 def attention_simple(q: torch.Tensor, out: torch.Tensor, kv, token_seq, slots, positions,
                      n_heads: int, scale: float, window: int = 0, value_dim: Optional[int] = None,
-                     chunk: int = 0, gate: Optional[torch.Tensor] = None) -> None:
+                     chunk: int = 0, gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                     sinks: Optional[torch.Tensor] = None, gate_logits: Optional[torch.Tensor] = None) -> None:
     """One warp per (token, head): the float32 path's attention, for prompts and
     decode steps alike.  `value_dim`: a value is the first so many channels of a
     row of the value plane (default: all of them), and a head of `out` is that wide.
     `chunk` > 0: a token sees the keys of its own stretch of `chunk` positions only.
-    `gate`: float32 [N, n_heads], a factor on each head's output."""
+    `gate`: float32 [N, n_heads], a factor on each head's output; `gate_logits`: float32
+    rows of n_heads * value width logits (any row stride) whose sigmoids multiply the
+    output channel by channel.  `softcap` c > 0: scores become c tanh(score / c).
+    `sinks`: float32 [n_heads]; exp(sinks[h]) joins head h's softmax denominator."""
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
     N = q.shape[0]
     vrow = kv.value_dim
@@ -904,23 +1058,41 @@ def attention_simple(q: torch.Tensor, out: torch.Tensor, kv, token_seq, slots, p
     _need(gate is None or (gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (N, n_heads)),
           "attention: gate must be contiguous float32 [N, n_heads]")
     _need(q.shape[1] >= n_heads * kv.head_dim and out.shape[1] >= n_heads * vd, "attention: q or out is too narrow")
+    gate_ld = 0
+    if gate_logits is not None:
+        _need(gate is None, "attention: a gate per head or logits per channel, not both")
+        _rows2d(gate_logits, "attention: gate_logits")
+        _need(gate_logits.dtype == torch.float32 and tuple(gate_logits.shape) == (N, n_heads * vd),
+              "attention: gate_logits must be float32 [N, n_heads * value width]")
+        gate, gate_ld = gate_logits, gate_logits.stride(0)
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads),
+          "attention: sinks must be contiguous float32 [n_heads]")
+    _need(softcap >= 0, "attention: the cap on the scores must not be negative")
     _check_access("attention_simple", 0, kv, slots, positions, token_seq, n_items=N)
     _check(_fn("gtg_attention_simple")(_dt(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0),
                                        _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
                                        kv.table_stride, _ptr(token_seq), _ptr(slots), _ptr(positions),
                                        N, n_heads, kv.n_kv_heads, kv.head_dim, vd, vrow, float(scale), int(window),
-                                       int(chunk), _ptr(gate), _stream()), "attention_simple")
+                                       int(chunk), _ptr(gate), int(gate_ld), float(softcap), _ptr(sinks), _stream()),
+           "attention_simple")
 
 
 def attention_general(q: torch.Tensor, out: torch.Tensor, kv, ctx, n_heads: int, scale: float, window: int = 0,
-                      chunk: int = 0, gate: Optional[torch.Tensor] = None) -> None:
+                      chunk: int = 0, gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                      gate_logits: Optional[torch.Tensor] = None) -> None:
     """Attention for mixers whose keys and values differ in size, whose keys are seen
     within stretches of `chunk` positions, or whose heads carry a gate: `ctx` is the
     step's context (rows, positions, sequences).  out[n, h] = gate[n, h] *
     softmax(q . K * scale over the visible keys) V.  bfloat16 heads of a multiple of 8
     channels up to 128 take the tensor-core kernel (`attention_masked_bf16`); float32
     and other widths the plain one; steps that bring more than one token a sequence, with
-    keys and values of 64 or 128 channels alike, the prompt attention on tcgen05."""
+    keys and values of 64 or 128 channels alike, the prompt attention on tcgen05.
+    `softcap` c > 0: scores become c tanh(score / c) after the scale.  `gate_logits`: float32
+    rows [N, n_heads * value width] whose sigmoids multiply the output channel by channel."""
+    if softcap or gate_logits is not None:
+        attention_simple(q, out, kv, ctx.token_seq, ctx.slots, ctx.positions, n_heads, scale, window, chunk=chunk, gate=gate,
+                         softcap=softcap, gate_logits=gate_logits)
+        return
     if (q.dtype == torch.bfloat16 and not ctx.is_decode and kv.value_dim == kv.head_dim and attention_tcgen05_supports(kv)
             and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
         attention_prefill_tcgen05(q, out, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, ctx.n_seqs, ctx.max_q_len, n_heads, scale,
@@ -1102,18 +1274,19 @@ def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: flo
 # ---------------------------------------------------------- attention through a latent
 def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], cos_sin: torch.Tensor, norm_weight: Optional[torch.Tensor],
                    eps: float, kv, token_seq, slots, positions, q_full: Optional[torch.Tensor], n_heads: int, dim: int,
-                   rot: int, rank: int, rows_out: Optional[torch.Tensor] = None) -> None:
+                   rot: int, rank: int, rows_out: Optional[torch.Tensor] = None, pairing: str = "interleaved") -> None:
     """Per token: with a down projection `dkv` [N, rank + rot], the latent
     rmsnorm(dkv[:, :rank]) * norm_weight and the rotated dkv[:, rank:] go into the
     token's cache row [rank + rot] of `kv`; and every head's rotated query part
     q[:, h, dim:] goes to q_full[:, h, rank:] (q [N, heads * (dim + rot)], q_full
     [N, heads * (rank + rot)]).  Of a rotated part's channels the first 2 P turn,
-    pairs (2i, 2i+1) by cos_sin [N, P, 2]; the rest pass unchanged.  Without q_full the
+    pairs (2i, 2i+1), or (i, i + P) with `pairing` "half", by cos_sin [N, P, 2]; the rest pass unchanged.  Without q_full the
     rotated query parts are written back into q.  `rows_out` [N, rank + rot], with a down
     projection, receives every token's cache row once more, token by token."""
     _rows2d(q, "latent_prepare: q")
     N = q.shape[0]
     _need(rot % 2 == 0 and rot > 0, "latent_prepare: an even number of rotated channels is needed")
+    _need(pairing in ROTARY_PAIRINGS, f"latent_prepare: pairing {pairing!r} is not known; known: {sorted(ROTARY_PAIRINGS)}")
     _need(q.shape[1] == n_heads * (dim + rot), "latent_prepare: q must be [N, heads*(dim+rot)]")
     if q_full is not None:
         _rows2d(q_full, "latent_prepare: q_full")
@@ -1141,7 +1314,8 @@ def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], cos_sin: torch.
     _check(_fn("gtg_latent_prepare")(_dt(q), _ptr(q), q.stride(0), _ptr(dkv), dkv.stride(0) if dkv is not None else 0,
                                      _ptr(cos_sin), _ptr(norm_weight), float(eps), *args, _ptr(token_seq), _ptr(slots),
                                      _ptr(positions), _ptr(q_full), q_full.stride(0) if q_full is not None else 0, N, n_heads, dim,
-                                     rot, rdims, rank, _ptr(rows_out), rows_out.stride(0) if rows_out is not None else 0, _stream()),
+                                     rot, rdims, rank, _ptr(rows_out), rows_out.stride(0) if rows_out is not None else 0,
+                                     ROTARY_PAIRINGS[pairing], _stream()),
            "latent_prepare")
 
 
@@ -1166,15 +1340,19 @@ def latent_attention_plan(n_seqs: int, max_q_len: int, n_heads: int, head_dim: i
 
 def latent_attention_bf16(q: torch.Tensor, out: torch.Tensor, kv, cu_seqlens, slots, start_pos, n_seqs: int,
                           max_q_len: int, n_heads: int, rank: int, scale: float, window: int = 0,
-                          n_splits: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+                          n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
+                          sinks: Optional[torch.Tensor] = None) -> None:
     """Attention of every (token, head) of the step over its sequence's cache rows
     (one shared head of kv.head_dim channels, the first `rank` of which are the
     values): q [N, heads * head_dim] folded query rows, out [N, heads * rank].
     Causal, over the last `window` keys (0: all).  Prompts, portions and single
     tokens alike.  With n_splits > 1 (`latent_attention_plan`) the keys are cut into
     runs whose results a second kernel merges; `scratch` then holds N times the
-    plan's floats per token."""
+    plan's floats per token.  `sinks`: float32 [n_heads]; exp(sinks[h]) joins head h's
+    softmax denominator without a key or a value."""
     _rows2d(q, "latent_attention: q"); _rows2d(out, "latent_attention: out")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads),
+          "latent_attention_bf16: sinks must be contiguous float32 [n_heads]")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and latent_attention_supports(kv, rank),
           "latent_attention_bf16: bfloat16 rows of a multiple of 16 channels, a multiple of 8 of them values")
     _need(q.shape[1] == n_heads * kv.head_dim and out.shape[1] == n_heads * rank and q.stride(0) % 8 == 0
@@ -1188,7 +1366,7 @@ def latent_attention_bf16(q: torch.Tensor, out: torch.Tensor, kv, cu_seqlens, sl
     _check(_fn("gtg_latent_attention_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), kv.page_stride,
                                             _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens), _ptr(slots), _ptr(start_pos),
                                             int(n_seqs), int(max_q_len), n_heads, kv.head_dim, int(rank), float(scale), int(window),
-                                            int(n_splits), _ptr(scratch) if n_splits > 1 else None, q.shape[0], _stream()),
+                                            int(n_splits), _ptr(scratch) if n_splits > 1 else None, q.shape[0], _ptr(sinks), _stream()),
            "latent_attention_bf16")
 
 
@@ -1209,12 +1387,16 @@ def latent_spread(k_rot: torch.Tensor, runs: torch.Tensor, n_heads: int, offset:
 
 
 def expanded_attention_bf16(q: torch.Tensor, runs: torch.Tensor, out: torch.Tensor, cu_seqlens, n_seqs: int, max_q_len: int,
-                            n_heads: int, dim: int, rot: int, v_dim: int, scale: float, window: int = 0) -> None:
+                            n_heads: int, dim: int, rot: int, v_dim: int, scale: float, window: int = 0,
+                            sinks: Optional[torch.Tensor] = None) -> None:
     """Attention of a step whose sequences all start at their first token, over the
     step's own rows with keys and values per head: q [N, heads * (dim + rot)] (a
     head's rotated part last, rotated); runs [N, heads * (dim + v_dim + rot)], per
     token and head [unrotated key | value | rotated key part] -> out [N, heads *
-    v_dim].  Causal within each sequence, over the last `window` keys (0: all)."""
+    v_dim].  Causal within each sequence, over the last `window` keys (0: all).  `sinks`:
+    float32 [n_heads], as in `latent_attention_bf16`."""
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads),
+          "expanded_attention_bf16: sinks must be contiguous float32 [n_heads]")
     for name, t in (("q", q), ("runs", runs), ("out", out)):
         _rows2d(t, f"expanded_attention: {name}")
         _need(t.dtype == torch.bfloat16, "expanded_attention_bf16: bfloat16 only")
@@ -1225,7 +1407,7 @@ def expanded_attention_bf16(q: torch.Tensor, runs: torch.Tensor, out: torch.Tens
     _int32("expanded_attention_bf16", cu_seqlens)
     _check(_fn("gtg_expanded_attention_bf16")(_ptr(q), q.stride(0), _ptr(runs), runs.stride(0), _ptr(out), out.stride(0),
                                               _ptr(cu_seqlens), int(n_seqs), int(max_q_len), n_heads, dim, rot, v_dim, float(scale),
-                                              int(window), _stream()), "expanded_attention_bf16")
+                                              int(window), _ptr(sinks), _stream()), "expanded_attention_bf16")
 
 
 # ------------------------------------------------------------------ routed experts

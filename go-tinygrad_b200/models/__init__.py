@@ -1,2 +1,2 @@
 """Architectures the library ships with.  Importing this package registers them."""
-from . import llama, ropovik, senupel, zotolix  # noqa: F401  (registration)
+from . import llama, megerax, ropovik, senupel, zotolix  # noqa: F401  (registration)

@@ -35,6 +35,22 @@ sigmoid(gate_h . x) before the output projection.  ``value_blend``: {"role":
 "source" layer leaves its values for the step under the key, a "blend" layer
 caches and attends (1 - w) v + w v_source for the same token (the source's own
 scalar exists in the checkpoint and is not read).
+
+A second family of options, which go together and not with the ones above
+except ``value_dim`` and the biases (`_forward_conv`; `ops.qkv_conv_finish` stands
+between projection and attention).  ``conv``: {"taps": n, "q": name, "k": name,
+"v": name}, tensors [channels, taps] whose last column is the current token's:
+every channel of the biased q, k and v passes a causal convolution over the last
+n tokens, zeros before the sequence's start, directly behind the projection; the
+sequence's last n - 1 projected rows are kept as per-sequence state.
+``qk_norm`` "weight" with ``q_norm`` and ``k_norm`` (tensor names, [head_dim]):
+an RMS norm with that weight on every query and key head, before the rotation,
+eps ``norm_eps``.  A position encoding with interleaved pairs.  ``softcap`` c:
+scores become c tanh(score / c) after the scale.  ``output_gate``: tensor name
+[n_heads * value_dim, hidden]; the concatenated heads are multiplied channel by
+channel by sigmoid(G x) before the output projection.  With ``own_kv`` False the
+layer has none of the key and value tensors and reads another run's cache with
+queries, convolution state, window and gate of its own.
 """
 from __future__ import annotations
 
@@ -43,7 +59,7 @@ from typing import List, Mapping, Optional
 
 import torch
 
-from ..cache import CacheHandle, KVRequest, Request
+from ..cache import CacheHandle, KVRequest, Request, StateRequest
 from ..kernels import ops
 from ..weights.binder import WeightSpec
 from .base import Mixer, Runtime, StepContext, build_part, emit_update, register_part
@@ -76,13 +92,22 @@ class GQAttention(Mixer):
         # ---- options of the general route
         self.value_dim = int(self.p.get("value_dim") or self.head_dim)
         self.v_width = self.n_kv * self.value_dim
-        biases = [self.p.get(k) for k in ("q_bias", "k_bias", "v_bias")]
+        biases = [self.p.get(k) for k in (("q_bias", "k_bias", "v_bias") if self.own_kv else ("q_bias",))]
         if any(biases) and not all(biases):
             raise ValueError("an attention mixer has biases on q, k and v or on none of them")
         self.bias_names = [str(b) for b in biases] if all(biases) else None
         self.qk_norm = self.p.get("qk_norm")
-        if self.qk_norm not in (None, "unit"):
-            raise ValueError(f"qk_norm {self.qk_norm!r} is not known: None or 'unit'")
+        if self.qk_norm not in (None, "unit", "weight"):
+            raise ValueError(f"qk_norm {self.qk_norm!r} is not known: None, 'unit' or 'weight'")
+        conv = self.p.get("conv")
+        self.conv = dict(conv) if conv and int(conv.get("taps", 0)) > 0 else None
+        self.taps = int(self.conv["taps"]) if self.conv else 1
+        cap = self.p.get("softcap")
+        self.softcap = float(cap) if cap else 0.0
+        out_gate = self.p.get("output_gate")
+        self.out_gate_name = str(out_gate) if out_gate else None
+        self.conv_route = bool(self.conv or self.qk_norm == "weight" or self.softcap or self.out_gate_name
+                               or self.position.pairing == "interleaved")
         self.norm_eps = float(self.p.get("norm_eps") or 0.0)
         chunk = self.p.get("chunk")
         self.chunk = int(chunk) if chunk else None
@@ -93,9 +118,18 @@ class GQAttention(Mixer):
         if self.blend and self.blend.get("role") not in ("source", "blend"):
             raise ValueError(f"value_blend role {self.blend.get('role')!r} is not known: 'source' or 'blend'")
         self.general = bool(self.value_dim != self.head_dim or self.bias_names or self.qk_norm or self.chunk
-                            or self.gate_name or self.blend)
-        if self.general and (self.v_from_k or not self.own_kv):
+                            or self.gate_name or self.blend or self.conv_route)
+        if self.conv_route and (self.qk_norm == "unit" or self.chunk or self.gate_name or self.blend or self.v_from_k):
+            raise ValueError("convolved projections, weighted head norms, capped scores and the gate on all channels are "
+                             "not built together with unit norms, stretches of keys, gates per head or blended values")
+        if self.general and (self.v_from_k or (not self.own_kv and not self.conv_route)):
             raise ValueError("the options of the general attention route need key and value projections of the layer's own")
+        self.norm_names = None
+        if self.qk_norm == "weight":
+            self.norm_names = [str(self.param("q_norm"))] + ([str(self.param("k_norm"))] if self.own_kv else [])
+        # channels that pass the convolution: q, and k and v where the layer has them
+        self.conv_channels = self.q_dim + ((self.kv_dim + self.v_width) if self.own_kv else 0)
+        self.conv_w = self.q_norm_w = self.k_norm_w = None
         self.bias: Optional[torch.Tensor] = None
         self.blend_weight = 0.0
         self.w_qkv: Optional[torch.Tensor] = None
@@ -111,6 +145,13 @@ class GQAttention(Mixer):
         if self.bias_names:
             specs += [WeightSpec(name, (size,), role="parameter", std=0.02)
                       for name, size in zip(self.bias_names, (self.q_dim, self.kv_dim, self.v_width))]
+        if self.conv:
+            specs += [WeightSpec(str(self.conv[k]), (size, self.taps), role="parameter", mean=1.0 / self.taps, std=0.3)
+                      for k, size in self._conv_parts()]
+        if self.norm_names:
+            specs += [WeightSpec(name, (self.head_dim,), role="vector", mean=1.0) for name in self.norm_names]
+        if self.out_gate_name:
+            specs.append(WeightSpec(self.out_gate_name, (self.n_heads * self.value_dim, self.hidden)))
         if self.gate_name:
             specs.append(WeightSpec(self.gate_name, (self.n_heads, self.hidden)))
         if self.blend:
@@ -119,10 +160,23 @@ class GQAttention(Mixer):
                                     optional=source, mean=0.3, std=0.1))
         return specs
 
+    def _conv_parts(self):
+        parts = [("q", self.q_dim)]
+        if self.own_kv:
+            parts += [("k", self.kv_dim), ("v", self.v_width)]
+        return parts
+
     def children(self):
         return [self.position]
 
     def cache_requests(self) -> List[Request]:
+        if self.conv_route:
+            requests: List[Request] = []
+            if self.own_kv:
+                requests.append(KVRequest(self.n_kv, self.head_dim, self.window, value_dim=self.value_dim))
+            if self.taps > 1:
+                requests.append(StateRequest("conv", (self.taps - 1, self.conv_channels), "float32"))
+            return requests
         if not self.own_kv:
             return []
         if self.general:
@@ -137,6 +191,8 @@ class GQAttention(Mixer):
                 parts.append(tensors[self.names["v"]])
         if self.gate_name:
             parts.append(tensors[self.gate_name])
+        if self.out_gate_name:
+            parts.append(tensors[self.out_gate_name])
         rows = sum(p.shape[0] for p in parts)
         if self.general and rows % 8:
             # whole groups of 8 rows, so that the products' float sums keep rows of a multiple of 32 bytes
@@ -147,6 +203,37 @@ class GQAttention(Mixer):
             self.bias = rt.vector(torch.cat([tensors[name].reshape(-1).to(torch.float32) for name in self.bias_names]))
         if self.blend and self.blend["role"] == "blend":
             self.blend_weight = float(tensors[str(self.blend["weight"])].to(torch.float32))
+        if self.conv:
+            # tap by tap, [taps, q | k | v]: neighbouring channels read neighbouring weights
+            self.conv_w = rt.vector(torch.cat([tensors[str(self.conv[k])].to(torch.float32) for k, _ in self._conv_parts()],
+                                              dim=0).t().contiguous())
+        if self.norm_names:
+            self.q_norm_w = rt.vector(tensors[self.norm_names[0]])
+            self.k_norm_w = rt.vector(tensors[self.norm_names[1]]) if self.own_kv else None
+
+    def _forward_conv(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
+        rt = ctx.rt
+        kv = cache.kv
+        n = x.shape[0]
+        sums = rt.empty(n, self.w_qkv.shape[0], dtype=torch.float32)
+        ops.linear(x, self.w_qkv, sums)
+        rotation = self.position.rotation(ctx)
+        q = rt.empty(n, self.q_dim)
+        state = cache.state("conv") if self.taps > 1 else None
+        ops.qkv_conv_finish(sums, self.bias, self.conv_w, state, ctx.cu_seqlens, self.q_norm_w, self.k_norm_w, self.norm_eps,
+                            rotation, self.position.pairing == "interleaved", self.n_heads, self.n_kv if self.own_kv else 0,
+                            self.head_dim, self.value_dim, kv, q, ctx.token_seq, ctx.slots, ctx.positions,
+                            store=cache.writes and self.own_kv)
+        if state is not None:
+            # the convolution has read what it needed of the old state: now the step's raw sums join it
+            ops.conv_state_update(sums[:, : self.conv_channels], state, ctx.cu_seqlens, ctx.slots, ctx.n_seqs)
+        ctx.trace("q_attn", q)
+        mixed = rt.empty(n, self.n_heads * self.value_dim)
+        logits = sums[:, self.conv_channels: self.conv_channels + self.n_heads * self.value_dim] if self.out_gate_name else None
+        ops.attention_general(q, mixed, kv, ctx, self.n_heads, self.scale, window=self.window or 0,
+                              softcap=self.softcap, gate_logits=logits)
+        ctx.trace("attn", mixed)
+        return emit_update(mixed, self.w_o, ctx)
 
     def _forward_general(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
         rt = ctx.rt
@@ -188,6 +275,8 @@ class GQAttention(Mixer):
         kv = cache.kv
         if kv is None or kv.n_kv_heads != self.n_kv or kv.head_dim != self.head_dim or kv.value_dim != self.value_dim:
             raise ValueError("attention was given a cache entry that does not match its heads")
+        if self.conv_route:
+            return self._forward_conv(x, ctx, cache)
         if self.general:
             return self._forward_general(x, ctx, cache)
         n = x.shape[0]

@@ -7,7 +7,8 @@ up product's float sums, in its epilogue).  Parameters:
 ``up``, ``down``.  The reference has no ungated feed-forward.
 
 ``swiglu``: dense gated feed-forward (SwiGLU): down(silu(gate(x)) * up(x)), silu(g) =
-g / (1 + exp(-g)) (model/llama.go:1361-1401, backends/simd/vec.go:52-59).
+g / (1 + exp(-g)) (model/llama.go:1361-1401, backends/simd/vec.go:52-59); with
+``activation`` "gelu_tanh" or "relu2" that function stands in silu's place on the gate.
 
 Parameters: ``hidden_size``, ``intermediate_size`` and the tensor names
 ``gate``, ``up``, ``down``, and optionally ``gate_bias``, ``up_bias``,
@@ -58,7 +59,12 @@ class SwiGLU(FeedForward):
         self.hidden = int(self.param("hidden_size"))
         self.inter = int(self.param("intermediate_size"))
         self.names = {k: str(self.param(k)) for k in ("gate", "up", "down")}
+        self.activation = str(self.p.get("activation") or "silu")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward activation {self.activation!r} is not known; known: {sorted(ops.ACTIVATIONS)}")
         biases = [self.p.get(k) for k in ("gate_bias", "up_bias", "down_bias")]
+        if any(biases) and self.activation != "silu":
+            raise ValueError("a gated feed-forward with biases uses the silu activation")
         if any(biases) and not all(biases):
             raise ValueError("a gated feed-forward has biases on all three projections or on none")
         self.bias_names = [str(b) for b in biases] if all(biases) else None
@@ -80,7 +86,8 @@ class SwiGLU(FeedForward):
         # bfloat16: gate and up rows interleaved in blocks of 8 so that the product's
         # epilogue can apply silu(gate) * up to its float accumulators and write the
         # activation directly; float32: gate rows then up rows, and a kernel of its own
-        self.fused = rt.dtype == torch.bfloat16 and self.inter % 8 == 0 and not self.bias_names
+        self.fused = (rt.dtype == torch.bfloat16 and self.inter % 8 == 0 and not self.bias_names
+                      and self.activation in ops.GATED_EPILOGUES)
         if self.bias_names:
             self.biases = [rt.vector(tensors[name]) for name in self.bias_names]
         if self.fused:
@@ -96,13 +103,13 @@ class SwiGLU(FeedForward):
             return self._forward_biased(x, ctx)
         act = rt.empty(n, self.inter)
         if self.fused:
-            ops.linear(x, self.w_gate_up, act, epilogue="swiglu")
+            ops.linear(x, self.w_gate_up, act, epilogue=ops.GATED_EPILOGUES[self.activation])
         else:
             gate_up = rt.empty(n, 2 * self.inter)
             ops.linear(x, self.w_gate_up, gate_up)
             ctx.trace("gate_pre", gate_up[:, : self.inter])
             ctx.trace("up", gate_up[:, self.inter:])
-            ops.swiglu(gate_up, act)
+            ops.swiglu(gate_up, act, self.activation)
         ctx.trace("gate_act", act)
         return emit_update(act, self.w_down, ctx)
 

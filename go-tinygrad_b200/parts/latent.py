@@ -33,7 +33,12 @@ rot_dim)^-1/2), ``eps`` (of the latent's norm), ``position`` (a rotary
 PartSpec over the rotated part: interleaved pairs; it may rotate fewer
 channels than rot_dim), ``own_kv`` (False: no down projection, the run reads
 another run's cache rows), and the tensor names ``q``, ``dkv``, ``dkv_norm``,
-``uk``, ``uv``, ``gate`` (None: no gate), ``o``.
+``uk``, ``uv``, ``gate`` (None: no gate), ``o``.  Options: the position part may
+pair channel i with i + rot.dims/2 instead ("half"); ``q_latent`` ({"rank": r,
+"down": name, "norm": name}): the queries come through a latent of their own,
+q = W_q rmsnorm(W_down x) with that norm's weight and ``eps``, and ``q`` is then
+[heads * (head_dim + rot_dim), r]; ``sinks`` (tensor name, [heads]): exp(sink_h)
+joins head h's softmax denominator, without a key or a value and unscaled.
 """
 from __future__ import annotations
 
@@ -65,8 +70,8 @@ class LatentAttention(Mixer):
         self.eps = float(self.param("eps"))
         self.own_kv = bool(self.p.get("own_kv", True))
         self.position = build_part("position", self.param("position"))
-        if self.position.pairing != "interleaved" or (self.position.rotary_dim or self.rot) > self.rot:
-            raise ValueError("latent attention rotates interleaved pairs within its rotated part")
+        if (self.position.rotary_dim or self.rot) > self.rot:
+            raise ValueError("latent attention rotates pairs within its rotated part")
         if self.rot % 2:
             raise ValueError(f"the rotated part needs an even number of channels, got {self.rot}")
         wanted = ["q", "uk", "uv", "o"] + (["dkv", "dkv_norm"] if self.own_kv else [])
@@ -74,6 +79,14 @@ class LatentAttention(Mixer):
         gate = self.p.get("gate")
         if gate:
             self.names["gate"] = str(gate)
+        q_latent = self.p.get("q_latent")
+        self.q_rank = int(q_latent["rank"]) if q_latent else 0
+        if q_latent:
+            self.names["q_down"], self.names["q_norm"] = str(q_latent["down"]), str(q_latent["norm"])
+        sinks = self.p.get("sinks")
+        if sinks:
+            self.names["sinks"] = str(sinks)
+        self.sinks = self.w_q_down = self.w_q_up = self.q_norm_w = None
         self.row = self.rank + self.rot                     # a cache row, and a folded query row of a head
         self.q_dim = self.n_heads * (self.dim + self.rot)
         self.g_dim = self.n_heads * self.v_dim if gate else 0
@@ -81,7 +94,12 @@ class LatentAttention(Mixer):
 
     def weight_specs(self) -> List[WeightSpec]:
         H = self.n_heads
-        specs = [WeightSpec(self.names["q"], (self.q_dim, self.hidden))]
+        specs = [WeightSpec(self.names["q"], (self.q_dim, self.q_rank or self.hidden))]
+        if self.q_rank:
+            specs += [WeightSpec(self.names["q_down"], (self.q_rank, self.hidden)),
+                      WeightSpec(self.names["q_norm"], (self.q_rank,), role="vector", mean=1.0)]
+        if "sinks" in self.names:
+            specs.append(WeightSpec(self.names["sinks"], (H,), role="parameter", std=1.0))
         if self.own_kv:
             specs += [WeightSpec(self.names["dkv"], (self.row, self.hidden)),
                       WeightSpec(self.names["dkv_norm"], (self.rank,), role="vector", mean=1.0)]
@@ -100,13 +118,19 @@ class LatentAttention(Mixer):
 
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         H = self.n_heads
-        parts = [tensors[self.names["q"]]]
+        parts = [] if self.q_rank else [tensors[self.names["q"]]]
+        if self.q_rank:
+            self.w_q_down = rt.matrix(tensors[self.names["q_down"]])
+            self.w_q_up = rt.matrix(tensors[self.names["q"]])
+            self.q_norm_w = rt.vector(tensors[self.names["q_norm"]])
+        if "sinks" in self.names:
+            self.sinks = rt.vector(tensors[self.names["sinks"]].reshape(-1))
         if "gate" in self.names:
             parts.append(tensors[self.names["gate"]])
         if self.own_kv:
             parts.append(tensors[self.names["dkv"]])
             self.norm_w = rt.vector(tensors[self.names["dkv_norm"]])
-        self.w_in = rt.matrix(torch.cat([p.to(rt.dtype) for p in parts], dim=0))
+        self.w_in = rt.matrix(torch.cat([p.to(rt.dtype) for p in parts], dim=0)) if parts else None
         # U_h^T per head, [H, rank, dim]: the product that folds U_h into the query reads it as its weight
         self.w_uk_t = rt.matrix(tensors[self.names["uk"]].to(rt.dtype).reshape(H, self.dim, self.rank).transpose(1, 2))
         self.w_uv = rt.matrix(tensors[self.names["uv"]]).view(H, self.v_dim, self.rank)
@@ -126,18 +150,31 @@ class LatentAttention(Mixer):
         if kv is None or kv.n_kv_heads != 1 or kv.head_dim != self.row:
             raise ValueError("latent attention was given a cache entry that does not hold its rows")
         n, H = x.shape[0], self.n_heads
-        width = self.w_in.shape[0]
-        proj = rt.empty(n, (width + 7) // 8 * 8)[:, :width]
-        ops.linear(x, self.w_in, proj)
-        q = proj[:, : self.q_dim]
-        gate = proj[:, self.q_dim: self.q_dim + self.g_dim] if self.g_dim else None
-        dkv = proj[:, self.q_dim + self.g_dim:] if (self.own_kv and cache.writes) else None
+        width = self.w_in.shape[0] if self.w_in is not None else 0
+        proj = rt.empty(n, (width + 7) // 8 * 8)[:, :width] if width else None
+        if width:
+            ops.linear(x, self.w_in, proj)
+        if self.q_rank:
+            # queries through their own latent: the down projection leaves float sums, the norm reads those
+            q_sums = rt.empty(n, self.q_rank, dtype=torch.float32)
+            ops.linear(x, self.w_q_down, q_sums)
+            cq = rt.empty(n, self.q_rank)
+            ops.add_rmsnorm(q_sums, None, self.q_norm_w, self.eps, cq)
+            q = rt.empty(n, (self.q_dim + 7) // 8 * 8)[:, : self.q_dim]
+            ops.linear(cq, self.w_q_up, q)
+            q_cols = 0
+        else:
+            q = proj[:, : self.q_dim]
+            q_cols = self.q_dim
+        gate = proj[:, q_cols: q_cols + self.g_dim] if self.g_dim else None
+        dkv = proj[:, q_cols + self.g_dim:] if (self.own_kv and cache.writes) else None
         rotation = self.position.rotation(ctx)
+        pairing = self.position.pairing
         if self._expands(ctx, cache):
             return self._forward_expanded(x, ctx, cache, q, gate, dkv, rotation)
         folded = rt.empty(n, H * self.row)
         ops.latent_prepare(q, dkv, rotation, self.norm_w, self.eps, kv, ctx.token_seq, ctx.slots, ctx.positions,
-                           folded, H, self.dim, self.rot, self.rank)
+                           folded, H, self.dim, self.rot, self.rank, pairing=pairing)
         ops.linear_heads(q.view(n, H, self.dim + self.rot)[:, :, : self.dim], self.w_uk_t,
                          folded.view(n, H, self.row)[:, :, : self.rank])
         ctx.trace("q_attn", folded)
@@ -147,11 +184,12 @@ class LatentAttention(Mixer):
                                                        self.window or 0)
             scratch = rt.empty(n * floats, dtype=torch.float32) if splits > 1 else None
             ops.latent_attention_bf16(folded, attended, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, ctx.n_seqs,
-                                      ctx.max_q_len, H, self.rank, self.scale, self.window or 0, splits, scratch)
+                                      ctx.max_q_len, H, self.rank, self.scale, self.window or 0, splits, scratch,
+                                      sinks=self.sinks)
         else:
             # float32, and row sizes the tensor-core kernel does not take
             ops.attention_simple(folded, attended, kv, ctx.token_seq, ctx.slots, ctx.positions, H, self.scale,
-                                 self.window or 0, value_dim=self.rank)
+                                 self.window or 0, value_dim=self.rank, sinks=self.sinks)
         heads = rt.empty(n, (H * self.v_dim + 7) // 8 * 8)[:, : H * self.v_dim]
         ops.linear_heads(attended.view(n, H, self.rank), self.w_uv, heads.view(n, H, self.v_dim),
                          gate.view(n, H, self.v_dim) if gate is not None else None)
@@ -178,18 +216,18 @@ class LatentAttention(Mixer):
         if dkv is not None:
             rows = rt.empty(n, self.row, lifetime="step")
             ops.latent_prepare(q, dkv, rotation, self.norm_w, self.eps, cache.kv, ctx.token_seq, ctx.slots, ctx.positions,
-                               None, H, self.dim, self.rot, self.rank, rows_out=rows)
+                               None, H, self.dim, self.rot, self.rank, rows_out=rows, pairing=self.position.pairing)
             ctx.shared[self._rows_key(cache)] = rows
         else:
             rows = ctx.shared[self._rows_key(cache)]
             ops.latent_prepare(q, None, rotation, None, self.eps, None, ctx.token_seq, ctx.slots, ctx.positions,
-                               None, H, self.dim, self.rot, self.rank)
+                               None, H, self.dim, self.rot, self.rank, pairing=self.position.pairing)
         runs = rt.empty(n, H * (self.dim + self.v_dim + self.rot))
         ops.linear(rows[:, : self.rank], self.w_expand, runs)
         ops.latent_spread(rows[:, self.rank:], runs, H, self.dim + self.v_dim)
         heads = rt.empty(n, H * self.v_dim)
         ops.expanded_attention_bf16(q, runs, heads, ctx.cu_seqlens, ctx.n_seqs, ctx.max_q_len, H, self.dim, self.rot,
-                                    self.v_dim, self.scale, self.window or 0)
+                                    self.v_dim, self.scale, self.window or 0, sinks=self.sinks)
         if gate is not None:
             ops.sigmoid_gate(heads, gate)
         return emit_update(heads, self.w_o, ctx)

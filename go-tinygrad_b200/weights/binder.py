@@ -28,11 +28,22 @@ class WeightSpec:
     # a recurrence or a convolution), but the random-weights mode draws it from
     # the spec's own 'std' and 'mean' whatever the caller asks for matrices and
     # norms; 'ignored' may be in the file but is never read.  'std' and 'mean'
-    # are what the random-weights mode draws from.
+    # are what the random-weights mode draws from.  A size of -1 in `shape` is
+    # left to the checkpoint (the part reads it from the tensor it is handed);
+    # the random-weights mode uses `free_size` there.
     role: str = "matrix"
     optional: bool = False
     std: float = 0.02
     mean: float = 0.0
+    free_size: int = 0
+
+    def fits(self, shape: Sequence[int]) -> bool:
+        return len(shape) == len(self.shape) and all(w == -1 or w == g for w, g in zip(self.shape, shape))
+
+    def drawn_shape(self) -> Tuple[int, ...]:
+        if -1 in self.shape and self.free_size <= 0:
+            raise ValueError(f"{self.name}: a size left to the checkpoint needs 'free_size' to be drawn at random")
+        return tuple(self.free_size if d == -1 else d for d in self.shape)
 
 
 class WeightError(ValueError):
@@ -87,7 +98,7 @@ def bind(source: TensorSource, specs: Iterable[WeightSpec], where: str = None,
                 missing.append(s.name)
             continue
         got = tuple(source.shape(s.name))
-        if got != tuple(s.shape):
+        if not s.fits(got):
             wrong_shape.append((s.name, tuple(s.shape), got))
         elif not source.dtype(s.name).is_floating_point:
             wrong_dtype.append((s.name, str(source.dtype(s.name))))

@@ -39,7 +39,7 @@ def random_tensors(specs, seed: int, std: Optional[float], norm_std: float,
         g = torch.Generator(device=device)
         g.manual_seed(_tensor_seed(seed, s.name))
         scale = norm_std if s.role == "vector" else s.std if (std is None or s.role == "parameter") else std
-        t = torch.randn(s.shape, generator=g, dtype=torch.float32, device=device)
+        t = torch.randn(s.drawn_shape(), generator=g, dtype=torch.float32, device=device)
         out[s.name] = (s.mean + scale * t).to(store_dtype)
     return out
 
