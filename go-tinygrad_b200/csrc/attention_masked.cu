@@ -19,7 +19,10 @@
 // log2(e)-scaled values; maximum, sum and the output accumulator are float.  Key
 // rows of hd and value rows of vd channels (multiples of 8) are zero-padded in
 // shared memory to DKP and DVP (64 or 128).  `gate` (or null) is a float factor per
-// (token, query head) on the output.
+// (token, query head) on the output; with `gate_ld` > 0 it holds one logit per output
+// channel instead (rows of gate_ld floats, heads side by side vd apart) and the factor is
+// the logit's sigmoid.  `softcap` c > 0: a scaled score s becomes c tanh(s / c) (the
+// hyperbolic tangent as 1 - 2 / (1 + e^(2x)): its error, times c, is far below a score's own).
 #include "mma_helpers.cuh"
 #include <math.h>
 
@@ -31,6 +34,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
+}
+
+// tanh(x) = 1 - 2 / (1 + e^(2x)); exact at both ends (e^(2x) = inf or 0), absolute error about 1e-7
+__device__ __forceinline__ float tanh_by_exp(float x) {
+    return 1.0f - __fdividef(2.0f, 1.0f + fast_exp2(x * (2.0f * kLog2e)));
 }
 
 __device__ __forceinline__ int first_seen(int pos, int window, int chunk) {
@@ -51,7 +59,7 @@ attention_masked_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
                         const int* __restrict__ start_pos,
                         int n_heads, int n_kv, int hd, int vd, float scale, int window, int chunk,
                         const float* __restrict__ gate, int n_splits,
-                        float* __restrict__ part_o, float* __restrict__ part_ml) {
+                        float* __restrict__ part_o, float* __restrict__ part_ml, float softcap, int gate_ld) {
     chain_release();
     chain_wait();
     constexpr int KCPR = DKP / 8, VCPR = DVP / 8;          // 16-byte chunks per staged row
@@ -141,7 +149,9 @@ attention_masked_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
     for (int i = 0; i < DVP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m_row[2] = {-INFINITY, -INFINITY};   // running max of scaled scores (log2 domain)
     float l_row[2] = {0.f, 0.f};               // this thread's share of the running sum
-    const float sl2 = scale * kLog2e;
+    // with a cap the scores are scaled and capped as they leave the product, and only log2(e) is left to multiply
+    const float sl2 = softcap > 0.f ? kLog2e : scale * kLog2e;
+    const float cap_in = softcap > 0.f ? scale / softcap : 0.f;
     // what every row of this warp sees of a page without looking closer: the first row's position
     // bounds the keys from above, the last row's first seen key from below
     const int w_first = tile * kTileRows + warp * 16, w_last = min(w_first + 15, tile * kTileRows + rows_here - 1);
@@ -188,6 +198,13 @@ attention_masked_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
                     ldmatrix_x4(b0, b1, b2, b3, kbase + swz_offset<DKP>(r, c));
                     mma_bf16_16816(s[jj * 2], qf[kk], b0, b1);
                     mma_bf16_16816(s[jj * 2 + 1], qf[kk], b2, b3);
+                }
+            }
+            if (softcap > 0.f) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[i][e] = softcap * tanh_by_exp(s[i][e] * cap_in);
                 }
             }
             // ---- mask by position (only pages that cross an edge for some row of this warp)
@@ -275,13 +292,20 @@ attention_masked_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
             if (t4 == 0) { part_ml[pidx * 2] = m_row[r]; part_ml[pidx * 2 + 1] = l_row[r]; }
             continue;
         }
-        const float inv = l_row[r] > 0.f ? (gate ? gate[th] : 1.0f) / l_row[r] : 0.f;
+        const float inv = l_row[r] > 0.f ? ((gate && gate_ld <= 0) ? gate[th] : 1.0f) / l_row[r] : 0.f;
         bf16* dst = out + (size_t)(q_begin + row_tok[r]) * ldo + (size_t)row_head[r] * vd;
+        const float* logits = (gate && gate_ld > 0) ? gate + (size_t)(q_begin + row_tok[r]) * gate_ld + (size_t)row_head[r] * vd : nullptr;
 #pragma unroll
         for (int i = 0; i < DVP / 8; ++i) {
             const int d = i * 8 + t4 * 2;
-            if (d < vd)
-                *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o[i][r * 2] * inv, o[i][r * 2 + 1] * inv);
+            if (d < vd) {
+                float a = o[i][r * 2] * inv, b = o[i][r * 2 + 1] * inv;
+                if (logits) {
+                    a *= 1.0f / (1.0f + expf(-logits[d]));
+                    b *= 1.0f / (1.0f + expf(-logits[d + 1]));
+                }
+                *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(a, b);
+            }
         }
     }
 }
@@ -289,7 +313,7 @@ attention_masked_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
 // One block per (token, query head): the shares in order, each scaled to the common maximum.
 __global__ void attention_masked_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               bf16* __restrict__ out, int ldo, const float* __restrict__ gate,
-                                              int n_heads, int vd, int dvp, int n_splits) {
+                                              int n_heads, int vd, int dvp, int n_splits, int gate_ld) {
     chain_release();
     chain_wait();
     const size_t th = blockIdx.x;
@@ -307,7 +331,7 @@ __global__ void attention_masked_merge_kernel(const float* __restrict__ part_o, 
             acc += f * part_o[pidx * dvp + d];
             L += f * part_ml[pidx * 2 + 1];
         }
-        const float gt = gate ? gate[th] : 1.0f;
+        const float gt = !gate ? 1.0f : gate_ld <= 0 ? gate[th] : 1.0f / (1.0f + expf(-gate[(size_t)n * gate_ld + (size_t)h * vd + d]));
         out[(size_t)n * ldo + (size_t)h * vd + d] = __float2bfloat16_rn(L > 0.f ? acc * gt / L : 0.f);
     }
 }
@@ -318,7 +342,7 @@ template <int DKP, int DVP>
 int launch_masked(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, const bf16* vc, long long page_stride,
                   const int* block_table, int table_stride, const int* cu_seqlens, const int* slots, const int* start_pos,
                   int n_seqs, int tiles, int n_heads, int n_kv, int hd, int vd, float scale, int window, int chunk,
-                  const float* gate, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                  const float* gate, int n_splits, float* part_o, float* part_ml, float softcap, int gate_ld, cudaStream_t stream) {
     auto kernel = attention_masked_kernel<DKP, DVP>;
     constexpr int smem = masked_smem_bytes<DKP, DVP>();
     static bool configured = false;
@@ -329,7 +353,7 @@ int launch_masked(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, co
     }
     return launch_chained(kernel, dim3(tiles * n_splits, n_kv, n_seqs), dim3(128), smem, stream, q, ldq, out, ldo, kc, vc,
                           page_stride, block_table, table_stride, cu_seqlens, slots, start_pos, n_heads, n_kv, hd, vd, scale,
-                          window, chunk, gate, n_splits, part_o, part_ml);
+                          window, chunk, gate, n_splits, part_o, part_ml, softcap, gate_ld);
 }
 }  // namespace
 
@@ -367,9 +391,11 @@ GTG_API int gtg_attention_masked_bf16(const void* q, int ldq, void* out, int ldo
                                       long long page_stride, const int* block_table, int table_stride,
                                       const int* cu_seqlens, const int* slots, const int* start_pos, int n_seqs, int max_q_len,
                                       int n_tokens, int n_heads, int n_kv, int hd, int vd, float scale, int window, int chunk,
-                                      const float* gate, int n_splits, float* scratch, cudaStream_t stream) {
+                                      const float* gate, int n_splits, float* scratch, float softcap, int gate_ld,
+                                      cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || window < 0 || chunk < 0 || n_splits < 1) return kErrBadArgument;
+    if (softcap < 0.f || (gate && gate_ld > 0 && gate_ld < n_heads * vd)) return kErrBadArgument;
     if (!gtg_attention_masked_supports(hd, vd)) return kErrUnsupported;
     if (n_splits > 1 && !scratch) return kErrBadArgument;
     if (ldq % 8 || page_stride % 8 || ((uintptr_t)q % 16) || ((uintptr_t)kc % 16) || ((uintptr_t)vc % 16) || ldo % 2 ||
@@ -383,12 +409,12 @@ GTG_API int gtg_attention_masked_bf16(const void* q, int ldq, void* out, int ldo
 #define GTG_MASKED(DKP, DVP)                                                                                          \
     launch_masked<DKP, DVP>((const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kc, (const bf16*)vc, page_stride,       \
                             block_table, table_stride, cu_seqlens, slots, start_pos, n_seqs, (int)tiles, n_heads, n_kv, \
-                            hd, vd, scale, window, chunk, gate, n_splits, part_o, part_ml, stream)
+                            hd, vd, scale, window, chunk, gate, n_splits, part_o, part_ml, softcap, gate_ld, stream)
     int st;
     if (padded(hd) == 64) st = dvp == 64 ? GTG_MASKED(64, 64) : GTG_MASKED(64, 128);
     else st = dvp == 64 ? GTG_MASKED(128, 64) : GTG_MASKED(128, 128);
 #undef GTG_MASKED
     if (st != 0 || n_splits == 1) return st;
     return launch_chained(attention_masked_merge_kernel, dim3((unsigned)((long long)n_tokens * n_heads)), dim3(dvp >= 128 ? 128 : 64),
-                          0, stream, (const float*)part_o, (const float*)part_ml, (bf16*)out, ldo, gate, n_heads, vd, dvp, n_splits);
+                          0, stream, (const float*)part_o, (const float*)part_ml, (bf16*)out, ldo, gate, n_heads, vd, dvp, n_splits, gate_ld);
 }

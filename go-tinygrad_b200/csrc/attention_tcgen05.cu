@@ -191,7 +191,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                             const int* __restrict__ start_pos,
                             int n_heads, int n_kv, float scale, int window, int chunk,
-                            const float* __restrict__ gate) {
+                            const float* __restrict__ gate, float softcap, int gate_ld) {
+    // softcap c > 0: a scaled score s becomes c tanh(s / c) as it leaves tensor memory.  gate_ld > 0: `gate`
+    // holds one float logit per output channel (rows of gate_ld, heads side by side) and the factor is its sigmoid.
     using S = Shape<HD>;
     constexpr int BK = S::BK;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -316,7 +318,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int pos = start + tile * BQ + r;                   // position of this query
         const int seen_from = chunk > 0 ? pos - pos % chunk : 0; // first key of this query's stretch
         const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-        const float sl2 = scale * kLog2e;
+        const float sl2 = softcap > 0.f ? kLog2e : scale * kLog2e;
+        const float cap_in = softcap > 0.f ? scale / softcap : 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         uint32_t sv[BK];
         bool ok = true;
@@ -331,6 +334,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free);                  // S_i is in registers: the tile takes S_{i+1}
+            if (softcap > 0.f) {
+                // tanh(x) = 1 - 2 / (1 + e^(2x)): exact at both ends, absolute error about 1e-7
+#pragma unroll
+                for (int c = 0; c < BK; ++c) {
+                    const float e2 = fast_exp2(__uint_as_float(sv[c]) * cap_in * (2.0f * kLog2e));
+                    sv[c] = __float_as_uint(softcap * (1.0f - __fdividef(2.0f, 1.0f + e2)));
+                }
+            }
             const bool all_visible = (key0 + BK - 1 <= pos) && (window <= 0 || key0 > pos - window) && key0 >= seen_from;
             if (!all_visible) {
 #pragma unroll
@@ -413,13 +424,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok) ok = __all_sync(full, mbar_wait<kTest>(pv_done, (uint32_t)(n_steps - 1) & 1u, abort_flag));
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-            const float factor = (gate && r < rows_here) ? gate[(size_t)(q_begin + tile * BQ + r) * n_heads + h] : 1.0f;
+            const float factor = (gate && gate_ld <= 0 && r < rows_here) ? gate[(size_t)(q_begin + tile * BQ + r) * n_heads + h] : 1.0f;
             const float inv = l_run > 0.f ? factor / l_run : 0.f;
             bf16* dst = out + (size_t)(q_begin + tile * BQ + r) * ldo + h * HD;
+            const float* logits = (gate && gate_ld > 0 && r < rows_here) ? gate + (size_t)(q_begin + tile * BQ + r) * gate_ld + h * HD : nullptr;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 tmem_ld32(tmem_o + lane_off + 32 * c, sv);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (logits) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        sv[e] = __float_as_uint(__uint_as_float(sv[e]) * (1.0f / (1.0f + __expf(-logits[32 * c + e]))));
+                }
                 if (r < rows_here) {
 #pragma unroll
                     for (int piece = 0; piece < 4; ++piece) {
@@ -475,7 +492,8 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long l
 template <int HD, bool kTest>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, bf16* out, int ldo, const int* block_table,
            int table_stride, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int max_q_len,
-           int n_heads, int n_kv, float scale, int window, int chunk, const float* gate, cudaStream_t stream) {
+           int n_heads, int n_kv, float scale, int window, int chunk, const float* gate, float softcap, int gate_ld,
+           cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, kTest>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -486,7 +504,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, bf16* out, int l
     dim3 grid(n_heads, B, (max_q_len + BQ - 1) / BQ);
     return launch_chained(attention_prefill_tc_kernel<HD, kTest>, grid, dim3(kThreads), (size_t)Shape<HD>::kSmemBytes, stream,
                           map_q, map_kv, out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos,
-                          n_heads, n_kv, scale, window, chunk, gate);
+                          n_heads, n_kv, scale, window, chunk, gate, softcap, gate_ld);
 }
 }  // namespace
 
@@ -507,9 +525,10 @@ GTG_API int gtg_attention_prefill_tcgen05(const void* q, int ldq, int n_tokens, 
                                           const int* block_table, int table_stride,
                                           const int* cu_seqlens, const int* slots, const int* start_pos,
                                           int B, int max_q_len, int n_heads, int n_kv, int hd,
-                                          float scale, int window, int chunk, const float* gate, cudaStream_t stream) {
+                                          float scale, int window, int chunk, const float* gate, float softcap, int gate_ld,
+                                          cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return 0;
-    if (window < 0 || chunk < 0) return kErrBadArgument;
+    if (window < 0 || chunk < 0 || softcap < 0.f || (gate && gate_ld > 0 && gate_ld < n_heads * hd)) return kErrBadArgument;
     if (hd != 64 && hd != 128) return kErrUnsupported;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return kErrBadArgument;
     if (ldq % 8 || ldo % 8 || ((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)kc % 16)) return kErrUnsupported;
@@ -524,7 +543,7 @@ GTG_API int gtg_attention_prefill_tcgen05(const void* q, int ldq, int n_tokens, 
     st = make_map(&map_kv, kc, (long long)n_pages * kv_rows, hd, hd, kPageTokens);
     if (st != 0) return st;
 #define GTG_ARGS map_q, map_kv, (bf16*)out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos, \
-                 B, max_q_len, n_heads, n_kv, scale, window, chunk, gate, stream
+                 B, max_q_len, n_heads, n_kv, scale, window, chunk, gate, softcap, gate_ld, stream
     if (g_test_waits) return hd == 64 ? launch<64, true>(GTG_ARGS) : launch<128, true>(GTG_ARGS);
     return hd == 64 ? launch<64, false>(GTG_ARGS) : launch<128, false>(GTG_ARGS);
 #undef GTG_ARGS

@@ -90,7 +90,7 @@ _SIGNATURES = {
     "gtg_attention_masked_scratch_floats": ("attention_masked", [_I, _I, _I, _I]),
     "gtg_attention_masked_splits": ("attention_masked", [_I, _I, _I, _I, _I, _I, _I]),
     "gtg_attention_masked_bf16": ("attention_masked", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
-                                                       _F, _I, _I, _P, _I, _P, _P]),
+                                                       _F, _I, _I, _P, _I, _P, _F, _I, _P]),
     "gtg_hyper_norm": ("hyper", [_I, _I, _P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P]),
     "gtg_qkv_finish": ("attention_prep", [_I, _P, _I, _P, _P, _I, _I, _F, _P, _P, _F, _P, _I, _P, _P, _P, _L, _P, _I, _P, _P, _P,
                                           _I, _I, _I, _I, _I, _P]),
@@ -109,7 +109,7 @@ _SIGNATURES = {
     "gtg_attention_tcgen05_supports": ("attention_tcgen05", [_I]),
     "gtg_attention_tcgen05_status": ("attention_tcgen05", []),
     "gtg_attention_prefill_tcgen05": ("attention_tcgen05", [_P, _I, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P,
-                                                            _I, _I, _I, _I, _I, _F, _I, _I, _P, _P]),
+                                                            _I, _I, _I, _I, _I, _F, _I, _I, _P, _F, _I, _P]),
     "gtg_argmax": ("sampling", [_P, _I, _I, _I, _P, _P]),
     "gtg_sample_temperature": ("sampling", [_P, _I, _I, _I, _F, _U, _P, _P, _P, _P]),
 }
@@ -1089,14 +1089,10 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kv, ctx, n_heads: int,
     keys and values of 64 or 128 channels alike, the prompt attention on tcgen05.
     `softcap` c > 0: scores become c tanh(score / c) after the scale.  `gate_logits`: float32
     rows [N, n_heads * value width] whose sigmoids multiply the output channel by channel."""
-    if softcap or gate_logits is not None:
-        attention_simple(q, out, kv, ctx.token_seq, ctx.slots, ctx.positions, n_heads, scale, window, chunk=chunk, gate=gate,
-                         softcap=softcap, gate_logits=gate_logits)
-        return
     if (q.dtype == torch.bfloat16 and not ctx.is_decode and kv.value_dim == kv.head_dim and attention_tcgen05_supports(kv)
             and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
         attention_prefill_tcgen05(q, out, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, ctx.n_seqs, ctx.max_q_len, n_heads, scale,
-                                  window, chunk, gate)
+                                  window, chunk, gate, softcap=softcap, gate_logits=gate_logits)
         return
     if q.dtype == torch.bfloat16 and attention_masked_supports(kv) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and scale > 0:
         splits = int(_fn("gtg_attention_masked_splits")(ctx.n_seqs, ctx.max_q_len, n_heads, kv.n_kv_heads, ctx.max_kv_len,
@@ -1106,9 +1102,10 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kv, ctx, n_heads: int,
             scratch = ctx.rt.empty(int(_fn("gtg_attention_masked_scratch_floats")(q.shape[0], n_heads, kv.value_dim, splits)),
                                    dtype=torch.float32)
         attention_masked_bf16(q, out, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, ctx.n_seqs, ctx.max_q_len, n_heads, scale,
-                              window, chunk, gate, splits, scratch)
+                              window, chunk, gate, splits, scratch, softcap=softcap, gate_logits=gate_logits)
         return
-    attention_simple(q, out, kv, ctx.token_seq, ctx.slots, ctx.positions, n_heads, scale, window, chunk=chunk, gate=gate)
+    attention_simple(q, out, kv, ctx.token_seq, ctx.slots, ctx.positions, n_heads, scale, window, chunk=chunk, gate=gate,
+                     softcap=softcap, gate_logits=gate_logits)
 
 
 def attention_masked_supports(kv) -> bool:
@@ -1118,16 +1115,26 @@ def attention_masked_supports(kv) -> bool:
 
 def attention_masked_bf16(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int, max_q_len: int, n_heads: int, scale: float,
                           window: int = 0, chunk: int = 0, gate: Optional[torch.Tensor] = None, n_splits: int = 1,
-                          scratch: Optional[torch.Tensor] = None) -> None:
+                          scratch: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                          gate_logits: Optional[torch.Tensor] = None) -> None:
     """The tensor-core form of `attention_general`: rows are (token, query head of a group)
     pairs, a block of 64 rows reads each page once for the group.  Prompts, portions and
     decode steps alike; `n_splits` > 1 cuts every tile's pages into that many shares, merged
-    through `scratch` (float32, `gtg_attention_masked_scratch_floats`)."""
+    through `scratch` (float32, `gtg_attention_masked_scratch_floats`).  `softcap` and
+    `gate_logits` as in `attention_simple`."""
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
     N = q.shape[0]
+    gate_ld = 0
+    if gate_logits is not None:
+        _need(gate is None, "attention: a gate per head or logits per channel, not both")
+        _rows2d(gate_logits, "attention: gate_logits")
+        _need(gate_logits.dtype == torch.float32 and tuple(gate_logits.shape) == (N, n_heads * kv.value_dim),
+              "attention: gate_logits must be float32 [N, n_heads * value width]")
+        gate, gate_ld = gate_logits, gate_logits.stride(0)
+    _need(softcap >= 0, "attention: the cap on the scores must not be negative")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16, "attention_masked_bf16: bfloat16 only")
     _need(q.shape[1] >= n_heads * kv.head_dim and out.shape[1] >= n_heads * kv.value_dim, "attention: q or out is too narrow")
-    _need(gate is None or (gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (N, n_heads)),
+    _need(gate is None or gate_ld > 0 or (gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (N, n_heads)),
           "attention: gate must be contiguous float32 [N, n_heads]")
     _need(scale > 0, "attention_masked_bf16: the scale must be positive")
     _int32("attention", cu_seqlens, slots, start_pos)
@@ -1139,7 +1146,8 @@ def attention_masked_bf16(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int,
     _check(_fn("gtg_attention_masked_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), _ptr(kv.v), kv.page_stride,
                                             _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens), _ptr(slots), _ptr(start_pos),
                                             int(n_seqs), int(max_q_len), N, n_heads, kv.n_kv_heads, kv.head_dim, kv.value_dim,
-                                            float(scale), int(window), int(chunk), _ptr(gate), int(n_splits), _ptr(scratch), _stream()),
+                                            float(scale), int(window), int(chunk), _ptr(gate), int(n_splits), _ptr(scratch),
+                                            float(softcap), int(gate_ld), _stream()),
            "attention_masked_bf16")
 
 
@@ -1169,12 +1177,22 @@ def attention_tcgen05_supports(kv) -> bool:
 
 def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int, max_q_len: int,
                               n_heads: int, scale: float, window: int = 0, chunk: int = 0,
-                              gate: Optional[torch.Tensor] = None) -> None:
+                              gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                              gate_logits: Optional[torch.Tensor] = None) -> None:
     """Prompt attention on tcgen05 (128 queries x one head per thread block).  `chunk` > 0:
     a query sees the keys of its own stretch of `chunk` positions only; `gate`: float32
-    [N, n_heads], a factor on each head's output."""
+    [N, n_heads], a factor on each head's output.  `softcap` and `gate_logits` as in
+    `attention_simple`."""
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
-    _need(gate is None or (gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (q.shape[0], n_heads)),
+    gate_ld = 0
+    if gate_logits is not None:
+        _need(gate is None, "attention: a gate per head or logits per channel, not both")
+        _rows2d(gate_logits, "attention: gate_logits")
+        _need(gate_logits.dtype == torch.float32 and tuple(gate_logits.shape) == (q.shape[0], n_heads * kv.head_dim),
+              "attention: gate_logits must be float32 [N, n_heads * value width]")
+        gate, gate_ld = gate_logits, gate_logits.stride(0)
+    _need(softcap >= 0, "attention: the cap on the scores must not be negative")
+    _need(gate is None or gate_ld > 0 or (gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (q.shape[0], n_heads)),
           "attention: gate must be contiguous float32 [N, n_heads]")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "attention_prefill_tcgen05: bfloat16 only")
     _need(attention_tcgen05_supports(kv),
@@ -1185,7 +1203,7 @@ def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: 
                                                 _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens),
                                                 _ptr(slots), _ptr(start_pos), n_seqs, max_q_len, n_heads,
                                                 kv.n_kv_heads, kv.head_dim, float(scale), int(window), int(chunk),
-                                                _ptr(gate), _stream()),
+                                                _ptr(gate), float(softcap), int(gate_ld), _stream()),
            "attention_prefill_tcgen05")
 
 

@@ -38,6 +38,14 @@ def _rotary(rot, head_dim: int, pairing: str) -> PartSpec:
                                "scaling": scaling})
 
 
+def _kept_window(cfg: MegeraxConfig, i: int):
+    """How many keys layer i's cache keeps: what the longest-sighted of the layers that read it sees
+    (itself and those whose ``kv_from`` names it); None, all keys, if one of them has no window."""
+    windows = [cfg.layers[i].mixer.window] + [layer.mixer.window for layer in cfg.layers
+                                              if layer.type == "attention" and layer.mixer.kv_from == i]
+    return None if any(w is None for w in windows) else max(windows)
+
+
 def _attention(cfg: MegeraxConfig, i: int) -> PartSpec:
     m, p = cfg.layers[i].mixer, f"l{i}.mix."
     own = m.kv_from is None
@@ -48,6 +56,7 @@ def _attention(cfg: MegeraxConfig, i: int) -> PartSpec:
               "qk_norm": "weight", "q_norm": p + "q.norm", "norm_eps": cfg.norm_eps}
     conv = {"taps": m.conv, "q": p + "q.conv"} if m.conv else None
     if own:
+        params["cache_window"] = _kept_window(cfg, i)
         params.update({"k": p + "k", "v": p + "v", "k_bias": p + "k.b", "v_bias": p + "v.b", "k_norm": p + "k.norm"})
         if conv:
             conv.update({"k": p + "k.conv", "v": p + "v.conv"})

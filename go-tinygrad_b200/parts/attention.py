@@ -50,7 +50,10 @@ scores become c tanh(score / c) after the scale.  ``output_gate``: tensor name
 [n_heads * value_dim, hidden]; the concatenated heads are multiplied channel by
 channel by sigmoid(G x) before the output projection.  With ``own_kv`` False the
 layer has none of the key and value tensors and reads another run's cache with
-queries, convolution state, window and gate of its own.
+queries, convolution state, window and gate of its own.  ``cache_window`` (where
+given): how many keys the cache keeps for this layer's storage instead of
+``window`` (None: all of them): a layer whose keys other layers read through
+longer windows, or through none, must keep what the longest-sighted of them sees.
 """
 from __future__ import annotations
 
@@ -77,6 +80,10 @@ class GQAttention(Mixer):
             raise ValueError(f"{self.n_heads} query heads cannot share {self.n_kv} key/value heads")
         window = self.p.get("window")
         self.window = int(window) if window else None
+        kept = self.p["cache_window"] if "cache_window" in self.p else window
+        self.cache_window = int(kept) if kept else None
+        if self.cache_window is not None and (self.window is None or self.cache_window < self.window):
+            raise ValueError(f"a cache that keeps {self.cache_window} keys cannot serve a window of {self.window or 'all'}")
         scale = self.p.get("scale")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.own_kv = bool(self.p.get("own_kv", True))
@@ -173,15 +180,15 @@ class GQAttention(Mixer):
         if self.conv_route:
             requests: List[Request] = []
             if self.own_kv:
-                requests.append(KVRequest(self.n_kv, self.head_dim, self.window, value_dim=self.value_dim))
+                requests.append(KVRequest(self.n_kv, self.head_dim, self.cache_window, value_dim=self.value_dim))
             if self.taps > 1:
                 requests.append(StateRequest("conv", (self.taps - 1, self.conv_channels), "float32"))
             return requests
         if not self.own_kv:
             return []
         if self.general:
-            return [KVRequest(self.n_kv, self.head_dim, self.window, value_dim=self.value_dim, chunk=self.chunk)]
-        return [KVRequest(self.n_kv, self.head_dim, self.window)]
+            return [KVRequest(self.n_kv, self.head_dim, self.cache_window, value_dim=self.value_dim, chunk=self.chunk)]
+        return [KVRequest(self.n_kv, self.head_dim, self.cache_window)]
 
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         parts = [tensors[self.names["q"]]]
@@ -196,7 +203,7 @@ class GQAttention(Mixer):
         rows = sum(p.shape[0] for p in parts)
         if self.general and rows % 8:
             # whole groups of 8 rows, so that the products' float sums keep rows of a multiple of 32 bytes
-            parts.append(torch.zeros((8 - rows % 8, self.hidden), dtype=parts[0].dtype))
+            parts.append(torch.zeros((8 - rows % 8, self.hidden), dtype=parts[0].dtype, device=parts[0].device))
         self.w_qkv = rt.matrix(torch.cat([p.to(rt.dtype) for p in parts], dim=0))
         self.w_o = rt.matrix(tensors[self.names["o"]])
         if self.bias_names:
