@@ -35,8 +35,10 @@ Llama path, each against the copy peak.  With --design senupel it does the same
 for the Senupel design (attention through a latent, dense and routed
 feed-forwards; see `senupel_shape`), and with --design zotolix for the Zotolix
 design (four copies of the hidden state, attention within stretches of
-positions, squared-relu experts; see `zotolix_shape`).  The default run is not
-changed by any of them.
+positions, squared-relu experts; see `zotolix_shape`), and with --design megerax
+for the Megerax design (attention with convolved projections, capped scores and
+a gate on all channels, attention through a latent with sinks, the gated delta
+rule; see `megerax_shape`).  The default run is not changed by any of them.
 
 Peaks come from MEASURED_PEAKS.json beside this file if present, else from the
 fallback figures of an earlier measurement on the same pool.  Inputs are larger
@@ -504,6 +506,24 @@ def zotolix_shape(width, heads, kv_heads, dim, experts, expert_ff, top, vocab=32
             "layers": [{"type": "attention_2" if i % 2 else "attention", "mixer": mixer(i), "mlp": routed} for i in range(8)]}
 
 
+def megerax_shape(width, heads, kv_heads, dim, ff, l_heads, l_rank, l_qrank, d_heads, vocab=32000):
+    """Eight layers: attention with keys of its own (a causal convolution of four taps over q, k and v, weighted head
+    norms, half of a head rotating under wavelength scaling, scores capped at 30, a window of 1,024, the gate on all
+    channels), attention through a latent with a query latent and sinks, the gated delta rule (heads of 128 x 128),
+    and attention that reads the first layer's keys; twice.  Every layer has a gated gelu feed-forward."""
+    rot = {"dims": dim // 2, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    att = lambda src: {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "conv": 4, "rot": rot,
+                       "softcap": 30.0, "mask": {"size": 1024}, **({"kv_from": src} if src is not None else {})}
+    lat = {"heads": l_heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": l_rank, "q_rank": l_qrank, "scale": 192 ** -0.5,
+           "rot": {"dims": 64, "base": 10000.0}}
+    dlt = {"heads": d_heads, "kv_heads": d_heads, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 128, "gate_rank": 128}
+    mlp = {"kind": "dense", "ff": ff}
+    four = lambda at: [{"type": "attention", "mixer": att(None), "mlp": mlp}, {"type": "latent_attention", "mixer": lat, "mlp": mlp},
+                       {"type": "channel_delta", "mixer": dlt, "mlp": mlp}, {"type": "attention", "mixer": att(at), "mlp": mlp}]
+    return {"architecture": "Megerax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+            "layers": four(0) + four(4)}
+
+
 DESIGN_SIZES = {
     # the layer sizes of Llama-3.2-1B / SmolLM2 (width 2048) and of Llama-3.1-8B (width 4096); the
     # recurrence has twice the width in its inner size, heads of 64 and a state of 128, as Mamba-2 models do
@@ -523,7 +543,17 @@ ZOTOLIX_SIZES = {
     "w2048": (zotolix_shape(2048, 32, 8, 64, 16, 2048, 4), dict(LLAMA_3P2_1B, num_hidden_layers=8, vocab_size=32000)),
     "w4096": (zotolix_shape(4096, 32, 8, 128, 16, 3584, 4), dict(LLAMA_3P1_8B, num_hidden_layers=8, vocab_size=32000)),
 }
+MEGERAX_SIZES = {
+    # the same two widths, heads and feed-forward sizes as the Llama layers beside them; the latent layers keep 512
+    # channels a token, the delta layers as many value channels as the width
+    "w2048": (megerax_shape(2048, 32, 8, 64, 8192, 16, 512, 768, 16), dict(LLAMA_3P2_1B, num_hidden_layers=8, vocab_size=32000)),
+    "w4096": (megerax_shape(4096, 32, 8, 128, 14336, 32, 512, 1536, 32), dict(LLAMA_3P1_8B, num_hidden_layers=8, vocab_size=32000)),
+}
 DESIGNS = {
+    "megerax": (MEGERAX_SIZES, "8 layers: attention with convolved projections, capped scores, a window of 1024 and a gate on all "
+                               "channels (two with keys of their own, two reading theirs), attention through a latent with sinks, "
+                               "the gated delta rule with heads of 128 x 128; a gated gelu feed-forward each; beside 8 Llama layers "
+                               "of equal width, heads and feed-forward size; vocabulary 32000"),
     "zotolix": (ZOTOLIX_SIZES, "8 layers of attention within stretches of 1024 and 8192 positions (unit-norm and gated in turn, biased "
                                "projections, values blended with the first layer's), mixtures of 16 squared-relu experts (4 to a token, "
                                "the router's sigmoid on the input), four copies of the hidden state, beside 8 Llama layers of equal "
@@ -738,6 +768,123 @@ def run_design(args):
             del cache
         return rows
 
+    def megerax_kernel_table(cfg):
+        """Each kernel the Megerax design added or extended, alone, at this size: a prompt of T tokens
+        and a decode step of 64 sequences after 1,024 tokens; the bytes it has to move against the copy
+        peak and, for products and attention, its FLOPs against the matrix peak.  Beside each the like
+        kernel of the Llama path (of the Ropovik path for the recurrence) at the same rows."""
+        from go_tinygrad_b200.cache import Cache, KVRequest
+        from go_tinygrad_b200.parts.base import StepContext
+        bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+        a, d = cfg["layers"][0]["mixer"], cfg["layers"][2]["mixer"]
+        H, heads, n_kv, hd, taps, window, cap = cfg["width"], a["heads"], a["kv_heads"], a["dim"], a["conv"], a["mask"]["size"], a["softcap"]
+        ff = cfg["layers"][0]["mlp"]["ff"]
+        dh, dd, dv, dtaps = d["heads"], d["dim"], d["vdim"], d["conv"]
+        rows = []
+
+        def add(name, rows_n, ms, nbytes, flops=0, like=None):
+            rows.append({"kernel": name, "rows": rows_n, "us": round(ms * 1e3, 2), "mb": round(nbytes / 1e6, 2),
+                         "of_copy_peak": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3),
+                         **({"tflops": round(flops / ms / 1e9, 1), "of_matrix_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)} if flops else {}),
+                         **({"like": like} if like else {})})
+        rnd = lambda *shape, dtype=bf: torch.randn(*shape, device=dev, dtype=f32).to(dtype)
+        for n, n_seqs, ctx_len, tag in ((T, 1, 0, "prompt"), (64, 64, prompt_len, "decode")):
+            per = n // n_seqs
+            rt = lib.parts.Runtime(dev, bf)
+            cache = Cache([[KVRequest(n_kv, hd, None, value_dim=hd)]], [None],
+                          max_tokens=64 * ((ctx_len + per + 63) // 64) * n_seqs, max_slots=n_seqs, dtype=bf, device=dev)
+            slot_list = [cache.open_sequence() for _ in range(n_seqs)]
+            cache.reserve_many([(s, ctx_len + per) for s in slot_list]); cache.flush_tables()
+            for g in cache.groups:
+                g.storage.normal_()
+            kv = cache.handles[0].kv
+            cu = torch.arange(0, n + 1, per, dtype=i32, device=dev)
+            seq = torch.arange(n, dtype=i32, device=dev) // per
+            slots = torch.tensor(slot_list, dtype=i32, device=dev)
+            start = torch.full((n_seqs,), ctx_len, dtype=i32, device=dev)
+            pos = (start[seq.long()] + (torch.arange(n, device=dev) % per)).to(i32)
+            ctx = StepContext(rt=rt, n_tokens=n, n_seqs=n_seqs, tokens=seq, positions=pos, token_seq=seq, cu_seqlens=cu, slots=slots,
+                              start_pos=start, max_q_len=per, max_kv_len=ctx_len + per, is_decode=per == 1, total_kv_len=n_seqs * (ctx_len + per))
+            # the norm behind the embedding, beside the norm before a sublayer
+            res, upd, w = rnd(n, H, dtype=f32), rnd(n, H), rnd(H, dtype=f32)
+            out = torch.empty(n, H, dtype=bf, device=dev)
+            add(f"rmsnorm_rows ({tag})", n, timed(lambda: ops.rmsnorm_rows(res, w, 1e-5)), n * H * 8)
+            add(f"add_rmsnorm ({tag})", n, timed(lambda: ops.add_rmsnorm(res, upd, w, 1e-5, out)), n * H * (4 + 4 + 2 + 2), like="rmsnorm_rows")
+            # bias, convolution, head norms, rotation and cache store, beside rotation and store alone
+            C = (heads + 2 * n_kv) * hd
+            sums, bias, cw = rnd(n, C + heads * hd, dtype=f32), rnd(C, dtype=f32), rnd(taps, C, dtype=f32)
+            state = torch.zeros(n_seqs, taps - 1, C, dtype=f32, device=dev)
+            nq, nk, cs = rnd(hd, dtype=f32), rnd(hd, dtype=f32), rnd(n, hd // 4, 2, dtype=f32)
+            q = torch.empty(n, heads * hd, dtype=bf, device=dev)
+            add(f"qkv_conv_finish ({tag})", n, timed(lambda: ops.qkv_conv_finish(sums, bias, cw, state, cu, nq, nk, 1e-5, cs, True, heads, n_kv, hd, hd, kv, q, seq, slots, pos)),
+                n * C * (4 + 2))
+            add(f"conv_state_update ({tag})", n, timed(lambda: ops.conv_state_update(sums[:, :C], state, cu, slots, n_seqs)), n_seqs * (taps - 1) * C * 8)
+            qkv, cs2 = rnd(n, C), rnd(n, hd // 2, 2, dtype=f32)
+            kv_plain = Cache([[KVRequest(n_kv, hd, None)]], [None], max_tokens=64 * ((ctx_len + per + 63) // 64) * n_seqs, max_slots=n_seqs, dtype=bf, device=dev)
+            for s in slot_list:
+                kv_plain.open_sequence()
+            kv_plain.reserve_many([(s, ctx_len + per) for s in slot_list]); kv_plain.flush_tables()
+            kv_plain.groups[0].storage.normal_()
+            kvl = kv_plain.handles[0].kv
+            add(f"rope_kv_store ({tag})", n, timed(lambda: ops.rope_kv_store(qkv, cs2, heads, n_kv, hd, kvl, seq, slots, pos)), n * C * (2 + 2), like="qkv_conv_finish")
+            # attention with capped scores, the window and the gate on all channels, beside attention over all keys
+            mixed = torch.empty(n, heads * hd, dtype=bf, device=dev)
+            logits = sums[:, C:]
+            keys = n_seqs * min(ctx_len + 1, window) if per == 1 else sum(min(i + 1, window) for i in range(per))
+            add(f"attention, capped, window {window}, gated ({tag})", n,
+                timed(lambda: ops.attention_general(q, mixed, kv, ctx, heads, hd ** -0.5, window=window, softcap=cap, gate_logits=logits)),
+                n * heads * hd * (2 + 2 + 4) + n_seqs * n_kv * min(ctx_len + per, window + per) * hd * 4, 4 * heads * keys * hd)
+            add(f"attention, window {window} alone ({tag})", n,
+                timed(lambda: ops.attention_general(q, mixed, kv, ctx, heads, hd ** -0.5, window=window)),
+                n * heads * hd * 4 + n_seqs * n_kv * min(ctx_len + per, window + per) * hd * 4, 4 * heads * keys * hd, like="attention, capped")
+            if per == 1:
+                splits, chunk, ring = ops.attention_decode_plan(n, heads, n_kv, hd, ctx_len + 1, window, n * (ctx_len + 1))
+                scratch = torch.empty(max(1, ops.attention_decode_scratch_floats(n, heads, hd, splits)), dtype=f32, device=dev)
+                fn = lambda: ops.attention_decode_bf16(q, mixed, kvl, slots, pos, heads, hd ** -0.5, window, splits, scratch, chunk_pages=chunk, ring_pages=ring)
+                add(f"split-KV decode attention, window {window} ({tag})", n, timed(fn),
+                    n * heads * hd * 4 + n_seqs * n_kv * min(ctx_len + per, window + per) * hd * 4, 4 * heads * keys * hd, like="attention, capped")
+            # the delta rule: convolution with silu, preparation, recurrence, norm and gate; beside the state-space recurrence
+            W = 2 * dh * dd + dh * dv
+            dsums, dcw = rnd(n, W + dh, dtype=f32), rnd(dtaps, W, dtype=f32)
+            dstate = torch.zeros(n_seqs, dtaps - 1, W, dtype=f32, device=dev)
+            qkv_f = torch.empty(n, W, dtype=f32, device=dev)
+            add(f"causal_conv_silu, float ({tag})", n,
+                timed(lambda: ops.causal_conv_silu(dsums[:, :W], dcw, None, dstate, qkv_f, seq, cu, slots, n_seqs=n_seqs, update_state=True, one_token_each=per == 1)),
+                n * W * 8)
+            decay, beta = rnd(n, dh * dd, dtype=f32), torch.empty(n, dh, dtype=f32, device=dev)
+            dtb, alog = rnd(dh * dd, dtype=f32), rnd(dh, dtype=f32)
+            raw = decay.clone()
+            def prep():
+                decay.copy_(raw)
+                ops.delta_prepare(qkv_f, decay, dtb, alog, dsums[:, W:], beta, dh, dh, dd, 1e-6, dd ** -0.5)
+            add(f"delta_prepare, with a copy of the decays before it ({tag})", n, timed(prep), n * (2 * dh * dd * 8 + dh * dd * 16))
+            S = torch.zeros(n_seqs, dh, dd, dv, dtype=f32, device=dev)
+            y = torch.empty(n, dh * dv, dtype=f32, device=dev)
+            add(f"delta_scan ({tag})", n, timed(lambda: ops.delta_scan(qkv_f, qkv_f[:, 2 * dh * dd:], decay, beta, S, y, cu, slots, n_seqs, dh, dh, dd, dv)),
+                n * (3 * dh * dd + 2 * dh * dv) * 4 + n_seqs * dh * dd * dv * 8)
+            gate_l, nw = rnd(n, dh * dv, dtype=f32), rnd(dv, dtype=f32)
+            outd = torch.empty(n, dh * dv, dtype=bf, device=dev)
+            add(f"head_norm_gate ({tag})", n, timed(lambda: ops.head_norm_gate(y, gate_l, nw, 1e-5, outd, dh)), n * dh * dv * (4 + 4 + 2))
+            # the like kernels of the state-space path at equal inner size: heads of 64, a state of 128
+            mh, mp, ms_, mg = dh * dv // 64, 64, 128, 8
+            xs, bc = rnd(n, mh * mp), rnd(n, mg * ms_, 2, dtype=f32)
+            dt_raw, dtb2, alog2, skip = rnd(n, mh), rnd(mh, dtype=f32), rnd(mh, dtype=f32), rnd(mh, dtype=f32)
+            S2 = torch.zeros(n_seqs, mh, ms_, mp, dtype=f32, device=dev)
+            y2 = torch.empty(n, mh * mp, dtype=f32, device=dev)
+            add(f"ssm_scan ({tag})", n, timed(lambda: ops.ssm_scan(xs, bc, dt_raw, dtb2, alog2, skip, S2, y2, cu, slots, n_seqs, mh, mg, ms_, mp, one_token_each=per == 1)),
+                n * (mh * mp * 6 + mg * ms_ * 8) + n_seqs * mh * ms_ * mp * 8, like="delta_scan")
+            z, gw = rnd(n, mh * mp), rnd(mh * mp, dtype=f32)
+            og = torch.empty(n, mh * mp, dtype=bf, device=dev)
+            add(f"gated_rmsnorm ({tag})", n, timed(lambda: ops.gated_rmsnorm(y2, z, gw, 1e-5, og, mg)), n * mh * mp * (4 + 2 + 2), like="head_norm_gate")
+            # the gated feed-forward's first product with gelu on the gate in its epilogue, beside silu
+            x, wgu = rnd(n, H), rnd(2 * ff, H)
+            act = torch.empty(n, ff, dtype=bf, device=dev)
+            fl = 2 * n * 2 * ff * H
+            add(f"gate/up product, gelu on the gate ({tag})", n, timed(lambda: ops.linear(x, wgu, act, epilogue="gated_gelu_tanh")), wgu.numel() * 2 + n * (H + ff) * 2, fl)
+            add(f"gate/up product, silu on the gate ({tag})", n, timed(lambda: ops.linear(x, wgu, act, epilogue="swiglu")), wgu.numel() * 2 + n * (H + ff) * 2, fl, like="gelu on the gate")
+            del cache, kv_plain
+        return rows
+
     def zotolix_kernel_table(cfg):
         """Each kernel the Zotolix design added or extended, alone, at this size: a prompt of T
         tokens and a decode step of 64 sequences at the last place of a stretch; the bytes it has to move
@@ -911,7 +1058,7 @@ def run_design(args):
     sampler.mark()
     sizes = {}
     design_sizes, what = DESIGNS[args.design]
-    table = {"senupel": senupel_kernel_table, "zotolix": zotolix_kernel_table}.get(args.design, kernel_table)
+    table = {"senupel": senupel_kernel_table, "zotolix": zotolix_kernel_table, "megerax": megerax_kernel_table}.get(args.design, kernel_table)
     for name in (args.sizes.split(",") if args.sizes else list(design_sizes)):
         design_cfg, llama_cfg = design_sizes[name]
         sizes[name] = {args.design: model_numbers(design_cfg), "llama": model_numbers(llama_cfg),

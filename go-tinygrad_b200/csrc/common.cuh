@@ -83,6 +83,18 @@ __device__ __forceinline__ float activate(float x, int kind) {
 // activation (code - kEpiActivation) applied to its float sums before they are rounded.
 constexpr int kEpiActivation = 16;
 constexpr int kActivations = 3;
+// Epilogue code 1 is the gated product over interleaved rows, silu(gate) * up; from this value on it is
+// the same with activation (code - kEpiGated) on the gate in silu's place.
+constexpr int kEpiGated = 32;
+__host__ __device__ __forceinline__ bool epi_is_gated(int code) {
+    return code == 1 || (code >= kEpiGated && code < kEpiGated + kActivations);
+}
+__host__ __device__ __forceinline__ bool epi_is_activation(int code) {
+    return code >= kEpiActivation && code < kEpiActivation + kActivations;
+}
+__device__ __forceinline__ float gate_activate(float g, int code) {
+    return code == 1 ? g / (1.0f + expf(-g)) : activate(g, code - kEpiGated);
+}
 
 static inline int launch_status() {
     return (int)cudaGetLastError();

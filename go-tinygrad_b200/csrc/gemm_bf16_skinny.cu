@@ -90,14 +90,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 template <typename OutT>
 __device__ __forceinline__ void store_feature(OutT* C, int ldc, int m, int n0, int r, int M, int N,
                                               float s, int epi) {
-    if (epi != 1) {                                   // plain, or (from kEpiActivation on) with a pointwise activation
-        if (epi >= kEpiActivation) s = activate(s, epi - kEpiActivation);
+    if (!epi_is_gated(epi)) {                         // plain, or (from kEpiActivation on) with a pointwise activation
+        if (epi_is_activation(epi)) s = activate(s, epi - kEpiActivation);
         if (m < M && n0 + r < N) C[(size_t)m * ldc + n0 + r] = from_f32<OutT>(s);
         return;
     }
     const float up = __shfl_down_sync(0xffffffffu, s, 8);
     if (r < 8 && m < M && n0 + r + 8 < N)
-        C[(size_t)m * ldc + (n0 >> 1) + r] = from_f32<OutT>(s / (1.0f + expf(-s)) * up);
+        C[(size_t)m * ldc + (n0 >> 1) + r] = from_f32<OutT>(gate_activate(s, epi) * up);
 }
 
 // grid = (ceil(N/16), S) with clusters of (1, S, 1): blockIdx.y is the CTA's
@@ -562,10 +562,9 @@ GTG_API int gtg_gemm_bf16_skinny_max_rows() { return 64; }
 GTG_API int gtg_gemm_bf16_skinny(const void* X, int ldx, const void* W, int ldw, void* C, int ldc,
                                  int out_f32, int M, int N, int K, int epilogue, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (epilogue != 0 && epilogue != 1 && !(epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations))
-        return kErrBadArgument;
-    if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
-    if (K <= 0 || ldx < K || ldw < K || ldc < (epilogue == 1 ? N / 2 : N)) return kErrBadArgument;
+    if (epilogue != 0 && !epi_is_gated(epilogue) && !epi_is_activation(epilogue)) return kErrBadArgument;
+    if (epi_is_gated(epilogue) && N % 16 != 0) return kErrUnsupported;
+    if (K <= 0 || ldx < K || ldw < K || ldc < (epi_is_gated(epilogue) ? N / 2 : N)) return kErrBadArgument;
     if (M > 64) return kErrUnsupported;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     if ((N + 15) / 16 > 0x7fffffff / 16) return kErrUnsupported;

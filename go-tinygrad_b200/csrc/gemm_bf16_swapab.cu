@@ -271,11 +271,11 @@ swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             } else {
                 acc = *reinterpret_cast<const float4*>(part + t * BR + lane * 4);
             }
-            if (epi >= kEpiActivation) {                  // the plain product with a pointwise activation on its sums
+            if (epi_is_activation(epi)) {                 // the plain product with a pointwise activation on its sums
                 acc.x = activate(acc.x, epi - kEpiActivation); acc.y = activate(acc.y, epi - kEpiActivation);
                 acc.z = activate(acc.z, epi - kEpiActivation); acc.w = activate(acc.w, epi - kEpiActivation);
             }
-            if (epi != 1) {
+            if (!epi_is_gated(epi)) {
                 const int f = n0 + lane * 4;
                 OutT* dst = C + (size_t)t * ldc + f;
                 if (vec_ok && f + 3 < N) {
@@ -304,7 +304,7 @@ swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     OutT* dst = C + (size_t)t * ldc + j;
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        if (j + i < (N >> 1)) dst[i] = from_f32<OutT>(g[i] / (1.0f + expf(-g[i])) * u[i]);
+                        if (j + i < (N >> 1)) dst[i] = from_f32<OutT>(gate_activate(g[i], epi) * u[i]);
                 }
             }
         }
@@ -412,10 +412,9 @@ GTG_API int gtg_gemm_bf16_swapab(const void* X, int ldx, const void* W, int ldw,
     (void)scratch;
     if (M <= 0 || N <= 0) return 0;
     if (M > 128) return kErrUnsupported;
-    if (epilogue != 0 && epilogue != 1 && !(epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations))
-        return kErrBadArgument;
-    if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
-    if (K <= 0 || ldx < K || ldw < K || ldc < (epilogue == 1 ? N / 2 : N)) return kErrBadArgument;
+    if (epilogue != 0 && !epi_is_gated(epilogue) && !epi_is_activation(epilogue)) return kErrBadArgument;
+    if (epi_is_gated(epilogue) && N % 16 != 0) return kErrUnsupported;
+    if (K <= 0 || ldx < K || ldw < K || ldc < (epi_is_gated(epilogue) ? N / 2 : N)) return kErrBadArgument;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     int slices, kb_per;
     plan(N, K, device_sms(), &slices, &kb_per);

@@ -169,8 +169,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const __grid_constant__ CUtensorMap map_c, int use_store_map,
                     OutT* __restrict__ C, int ldc, int M, int N, int K, int epi_code, RopeKV rope, Grouping grp) {
     // a code from kEpiActivation on is the plain product (0) with a pointwise activation on its sums
-    const int act = epi_code >= kEpiActivation ? epi_code - kEpiActivation + 1 : 0;
-    const int epi = act ? 0 : epi_code;
+    const int act = epi_is_activation(epi_code) ? epi_code - kEpiActivation + 1 : 0;
+    const int epi = act ? 0 : epi_is_gated(epi_code) ? 1 : epi_code;    // a gated product whatever stands on its gate
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;        // tiles need 1024-byte alignment
     unsigned char* aligned = smem_raw + (base - smem_addr(smem_raw));
@@ -432,8 +432,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 for (int q = 0; q < 4; ++q) {
                                     const float g0 = __uint_as_float(v[16 * blk + 2 * q]), u0 = __uint_as_float(v[16 * blk + 8 + 2 * q]);
                                     const float g1 = __uint_as_float(v[16 * blk + 2 * q + 1]), u1 = __uint_as_float(v[16 * blk + 9 + 2 * q]);
-                                    __nv_bfloat162 h = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0,
-                                                                             g1 / (1.0f + __expf(-g1)) * u1);
+                                    __nv_bfloat162 h = epi_code == 1 ? __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0,
+                                                                                             g1 / (1.0f + __expf(-g1)) * u1)
+                                                                     : __floats2bfloat162_rn(gate_activate(g0, epi_code) * u0,
+                                                                                             gate_activate(g1, epi_code) * u1);
                                     p[q] = *reinterpret_cast<uint32_t*>(&h);
                                 }
                                 const int chunk = 2 * cc + blk;
@@ -474,7 +476,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {
                                 const float g = __uint_as_float(v[16 * blk + q]), u = __uint_as_float(v[16 * blk + 8 + q]);
-                                o[8 * blk + q] = __float_as_uint(g / (1.0f + __expf(-g)) * u);
+                                o[8 * blk + q] = __float_as_uint((epi_code == 1 ? g / (1.0f + __expf(-g)) : gate_activate(g, epi_code)) * u);
                             }
                         store_values<OutT, 16>(C + (size_t)row * ldc + (col >> 1), o, min(16, (N - col) / 2), vec_ok);
                     }
@@ -540,7 +542,9 @@ namespace {
 int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_f32, int M, int N, int K,
         int epilogue, const RopeKV& rope, cudaStream_t stream, const Grouping& grp = Grouping{nullptr, 0}, int n_experts = 1) {
     if (M <= 0 || N <= 0) return 0;
-    const bool with_activation = epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations;
+    const bool with_activation = epi_is_activation(epilogue);
+    const int epi_code = epilogue;                       // what the kernel is told
+    if (epi_is_gated(epilogue)) epilogue = 1;            // from here on: the gated product, whatever stands on its gate
     if ((epilogue < 0 || epilogue > 3) && !with_activation) return kErrBadArgument;
     if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
     if (epilogue == 3 && (!out_f32 || ldc % 4 || ((uintptr_t)C % 16))) return kErrUnsupported;
@@ -594,25 +598,25 @@ int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int ou
     if (g_test_waits) {
         if (out_f32)
             return launch_chained(gemm_tcgen05_kernel<float, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                                  map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue, rope, grp);
+                                  map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epi_code, rope, grp);
         return launch_chained(gemm_tcgen05_kernel<bf16, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                              map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue, rope, grp);
+                              map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epi_code, rope, grp);
     }
     if (out_f32)
         return launch_chained(gemm_tcgen05_kernel<float, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                              map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue, rope, grp);
+                              map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epi_code, rope, grp);
     return launch_chained(gemm_tcgen05_kernel<bf16, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                          map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue, rope, grp);
+                          map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epi_code, rope, grp);
 }
 }  // namespace
 
 // epilogue 0: C[M,N] = A W^T.  epilogue 1: W's rows come in blocks of 8 gate
 // features followed by their 8 up features, and C[M,N/2] = silu(gate) * up.
 // epilogue kEpiActivation + kind: C[M,N] = activation(A W^T), applied to the float sums.
+// epilogue kEpiGated + kind: as epilogue 1 with that activation on the gate in silu's place.
 GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
                                   int out_f32, int M, int N, int K, int epilogue, cudaStream_t stream) {
-    if (epilogue != 0 && epilogue != 1 && !(epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations))
-        return kErrBadArgument;
+    if (epilogue != 0 && !epi_is_gated(epilogue) && !epi_is_activation(epilogue)) return kErrBadArgument;
     return run(A, lda, W, ldw, C, ldc, out_f32, M, N, K, epilogue, RopeKV{}, stream);
 }
 
@@ -622,8 +626,7 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
 GTG_API int gtg_gemm_bf16_tcgen05_grouped(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
                                           int out_f32, int M, int N, int K, int epilogue, const int* tile_expert,
                                           int n_experts, cudaStream_t stream) {
-    if (epilogue != 0 && epilogue != 1 && !(epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations))
-        return kErrBadArgument;
+    if (epilogue != 0 && !epi_is_gated(epilogue) && !epi_is_activation(epilogue)) return kErrBadArgument;
     if (!tile_expert || n_experts <= 0 || M % BM) return kErrBadArgument;
     if ((long long)N * n_experts > 0x7fffffffLL) return kErrUnsupported;
     return run(A, lda, W, ldw, C, ldc, out_f32, M, N, K, epilogue, RopeKV{}, stream, Grouping{tile_expert, N}, n_experts);

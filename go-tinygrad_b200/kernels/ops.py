@@ -62,7 +62,7 @@ _SIGNATURES = {
                                                _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_delta_prepare": ("delta", [_P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P]),
     "gtg_delta_scan_supports": ("delta", [_I, _I]),
-    "gtg_delta_scan": ("delta", [_P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_delta_scan": ("delta", [_P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_head_norm_gate": ("delta", [_I, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _I, _P]),
     "gtg_rmsnorm_add": ("elementwise", [_I, _I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
     "gtg_round_rows": ("elementwise", [_I, _P, _P, _L, _P]),
@@ -400,7 +400,9 @@ def add_layernorm(residual: torch.Tensor, pending: Optional[torch.Tensor], weigh
 
 
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
-GATED_EPILOGUES = {"silu": "swiglu"}     # gate activations whose product act(gate) * up the products' epilogues form
+# gate activations whose product act(gate) * up the products' epilogues form, and the epilogue's name
+GATED_EPILOGUES = {"silu": "swiglu", "gelu_tanh": "gated_gelu_tanh", "relu2": "gated_relu2"}
+EPILOGUE_GATED = 32           # a product's epilogue code from here on: the gated product with activation (code - 32) on the gate
 EPILOGUE_ACTIVATION = 16      # a product's epilogue code from here on: the plain product, then activation (code - 16)
 
 
@@ -667,12 +669,13 @@ def delta_prepare(qk: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor, 
 
 def delta_scan(qk: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
                out: torch.Tensor, cu_seqlens, slots, n_seqs: int, n_heads: int, n_groups: int, key_dim: int,
-               value_dim: int) -> None:
+               value_dim: int, one_token_each: bool = False) -> None:
     """The gated delta rule, token by token, all float32: per head h (queries and keys of
     group h // (n_heads / n_groups)), S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T;
     out = S^T q.  qk [N, >= 2 groups * d] (queries, then keys), v [N, heads * dv], decay
     [N, heads * d], beta [N, heads]; state [slots, heads, d, dv], read and left per
-    sequence; out [N, heads * dv]."""
+    sequence; out [N, heads * dv].  `one_token_each`: row b is sequence b's only token (a
+    decode step), which a kernel of its own serves where the sizes allow."""
     for name, t in (("qk", qk), ("v", v), ("decay", decay), ("out", out)):
         _rows2d(t, f"delta_scan: {name}")
         _need(t.dtype == torch.float32, f"delta_scan: {name} must be float32")
@@ -688,7 +691,8 @@ def delta_scan(qk: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: tor
     _int32("delta_scan", cu_seqlens, slots)
     _check(_fn("gtg_delta_scan")(_ptr(qk), qk.stride(0), _ptr(v), v.stride(0), _ptr(decay), decay.stride(0), _ptr(beta),
                                  _ptr(state), _ptr(out), out.stride(0), _ptr(cu_seqlens), _ptr(slots), int(n_seqs),
-                                 n_heads, n_groups, key_dim, value_dim, _stream()), "delta_scan")
+                                 n_heads, n_groups, key_dim, value_dim, 1 if one_token_each and N == n_seqs else 0, _stream()),
+           "delta_scan")
 
 
 def head_norm_gate(y: torch.Tensor, gate_logits: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -835,7 +839,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
     the tokens as the N dimension, up to 128 rows), "tcgen05" (TMA + tensor memory)
     or "tiled" (warp-level MMA).  epilogue="swiglu" (bfloat16, not "tiled"): w is laid out by
     `interleave_gate_up` and out[M, N/2] = silu(gate) * up, computed from the
-    float accumulators.  epilogue="relu2" | "gelu_tanh" | "silu": out[M, N] is that
+    float accumulators; epilogue="gated_gelu_tanh" | "gated_relu2": the same with that
+    activation on the gate.  epilogue="relu2" | "gelu_tanh" | "silu": out[M, N] is that
     activation of the product, applied to the float sums inside the tensor-core
     kernels, by the `activation` kernel behind the others."""
     _rows2d(x, "linear: x"); _rows2d(w, "linear: w"); _rows2d(out, "linear: out")
@@ -849,8 +854,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
             linear(x, w, out, kind=kind)
             activation(out, epilogue)
             return
-    _need(epilogue in ("none", "swiglu") or epilogue in ACTIVATIONS, f"linear: unknown epilogue {epilogue!r}")
-    n_out = N // 2 if epilogue == "swiglu" else N
+    gated = epilogue in GATED_EPILOGUES.values()
+    _need(epilogue == "none" or gated or epilogue in ACTIVATIONS, f"linear: unknown epilogue {epilogue!r}")
+    n_out = N // 2 if gated else N
     _need(w.shape[1] == K and tuple(out.shape) == (M, n_out),
           f"linear: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} (epilogue {epilogue})")
     if x.dtype == torch.float32:
@@ -882,20 +888,21 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
         most = WARP_LEVEL_MAX_ROWS if kind == "skinny" else SKINNY_MAX_ROWS
         _need(M <= most, f"linear: the weight-streaming kernel {kind!r} takes at most {most} rows")
     out_f32 = 1 if out.dtype == torch.float32 else 0
-    epi_code = 1 if epilogue == "swiglu" else EPILOGUE_ACTIVATION + ACTIVATIONS[epilogue] if epilogue in ACTIVATIONS else 0
+    epi_code = (1 if epilogue == "swiglu" else EPILOGUE_GATED + ACTIVATIONS[epilogue[len("gated_"):]] if gated
+                else EPILOGUE_ACTIVATION + ACTIVATIONS[epilogue] if epilogue in ACTIVATIONS else 0)
     if kind == "tiled":
         _need(epilogue == "none", "linear: the warp-level kernel has no fused epilogue")
         code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
                            out_f32, M, N, K, _stream())
     elif kind == "swapab":
-        if epilogue == "swiglu":
+        if gated:
             _need(N % 16 == 0, f"linear: the fused SwiGLU needs a multiple of 16 rows of w, got {N}")
         scratch = torch.empty(int(_fn("gtg_gemm_bf16_swapab_scratch_floats")(M, N, K)), dtype=torch.float32,
                               device=x.device)
         code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
                            out_f32, M, N, K, epi_code, _ptr(scratch), _stream())
     else:
-        if epilogue == "swiglu":
+        if gated:
             _need(N % 16 == 0, f"linear: the fused SwiGLU needs a multiple of 16 rows of w, got {N}")
         code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
                            out_f32, M, N, K, epi_code, _stream())

@@ -261,7 +261,7 @@ class GatedDelta(Mixer):
                           self.unit_eps, self.dim ** -0.5)
         y = rt.empty(n, self.v_width, dtype=torch.float32)
         ops.delta_scan(qkv, qkv[:, self.qk_width:], decay, beta, cache.state("delta"), y, ctx.cu_seqlens, ctx.slots,
-                       ctx.n_seqs, self.n_heads, self.n_kv, self.dim, self.vdim)
+                       ctx.n_seqs, self.n_heads, self.n_kv, self.dim, self.vdim, one_token_each=ctx.is_decode)
         ctx.trace("scan", y)
         out = rt.empty(n, (self.v_width + 7) // 8 * 8)[:, : self.v_width]
         ops.head_norm_gate(y, gate, self.norm_w, self.eps, out, self.n_heads)

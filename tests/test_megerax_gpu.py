@@ -367,6 +367,45 @@ def test_the_delta_rule_carries_its_state_across_portions_and_slots(dtype, heads
     close(np.concatenate(got_y), want_y, dtype, "second of two", loose=2.0)
 
 
+@pytest.mark.parametrize("d,n_seqs", [(64, 37), (64, 19), (64, 10), (64, 2), (128, 19), (128, 10), (128, 3), (256, 10), (256, 2),
+                                      (96, 3), (16, 40)])
+def test_the_recurrence_kernels_for_every_split_of_the_state(d, n_seqs):
+    """The recurrence alone, for every number of lanes that share a column of the state (the launcher picks it
+    by how many columns a step brings): unequal sequences in one step, a second step that continues them, then a
+    step of one token each; every sequence against the plain recurrence, head by head."""
+    rng = np.random.default_rng(d + n_seqs)
+    H, G, dv = 8, 4, 64
+    lens = [[1 + (b + k) % 5 for b in range(n_seqs)] for k in range(2)] + [[1] * n_seqs]
+    total = [sum(l[b] for l in lens) for b in range(n_seqs)]
+    q = rng.standard_normal((n_seqs, max(total), G, d)); q /= np.linalg.norm(q, axis=-1, keepdims=True) * np.sqrt(d)
+    k = rng.standard_normal((n_seqs, max(total), G, d)); k /= np.linalg.norm(k, axis=-1, keepdims=True)
+    v = rng.standard_normal((n_seqs, max(total), H, dv))
+    g = rng.uniform(0.05, 1.0, (n_seqs, max(total), H, d))
+    beta = rng.uniform(0.0, 1.0, (n_seqs, max(total), H))
+    state = torch.zeros(n_seqs + 1, H, d, dv, dtype=torch.float32, device=DEV)
+    slots = torch.tensor([n_seqs - b for b in range(n_seqs)], dtype=torch.int32, device=DEV)       # not in order, slot 0 unused
+    got = [[] for _ in range(n_seqs)]
+    at = [0] * n_seqs
+    for step_lens in lens:
+        rows = lambda a, width: np.concatenate([a[b, at[b]:at[b] + step_lens[b]].reshape(step_lens[b], width) for b in range(n_seqs)])
+        qk = t32(np.concatenate([rows(q, G * d), rows(k, G * d)], axis=1))
+        vt, gt, bt = t32(rows(v, H * dv)), t32(rows(g, H * d)), t32(rows(beta, H))
+        out = torch.empty(sum(step_lens), H * dv, dtype=torch.float32, device=DEV)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(step_lens)]), dtype=torch.int32, device=DEV)
+        ops.delta_scan(qk, vt, gt, bt, state, out, cu, slots, n_seqs, H, G, d, dv, one_token_each=max(step_lens) == 1)
+        o = f64(out)
+        for b in range(n_seqs):
+            got[b].append(o[int(cu[b]):int(cu[b + 1])])
+            at[b] += step_lens[b]
+    for b in range(0, n_seqs, max(1, n_seqs // 4)):
+        T = total[b]
+        f = lambda a: f64(t32(a))
+        for h in range(H):
+            want = plain.delta_rule(f(q[b, :T, h // 2]), f(k[b, :T, h // 2]), f(v[b, :T, h]), f(beta[b, :T, h]), f(g[b, :T, h]))
+            close(np.concatenate(got[b])[:, h * dv:(h + 1) * dv], want, "float32", (d, n_seqs, b, h), loose=2.0)
+    assert float(state[0].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_the_delta_rule_remembers_its_first_token_where_it_does_not_decay(dtype):
     """Head 0 forgets almost nothing (a rate of e^-12), head 1 forgets within a few tokens.  The first
