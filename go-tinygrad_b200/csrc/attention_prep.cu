@@ -318,6 +318,115 @@ qkv_conv_finish_kernel(const float* __restrict__ sums, int ld, const float* __re
         __syncwarp();                                        // before the warp's next head overwrites x
     }
 }
+// The same for the many tokens of a prompt: a warp takes one head of kRunTokens consecutive rows.  The
+// rows a channel's taps reach, this step's kRunTokens + TAPS - 1 of them, are read once into registers and
+// serve all of the run's tokens, as do the channel's taps and bias; a row that belongs to another sequence
+// (or lies before the step) is never used: such a tap reads the state, or nothing, exactly as above.
+// The arithmetic and its order are those of the kernel above: their results are the same bits.
+constexpr int kRunTokens = 4;
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(kFinishWarps * 32)
+qkv_conv_finish_run_kernel(const float* __restrict__ sums, int ld, const float* __restrict__ bias,
+                           const float* __restrict__ conv_w, const float* __restrict__ conv_state,
+                           const int* __restrict__ cu_seqlens,
+                           const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                           const float2* __restrict__ cos_sin, int rot, int interleaved,
+                           T* __restrict__ q_out, int ldq, T* __restrict__ kc, T* __restrict__ vc, long long page_stride,
+                           const int* __restrict__ block_table, int table_stride,
+                           const int* __restrict__ token_seq, const int* __restrict__ slots,
+                           const int* __restrict__ positions, int N, int n_heads, int n_kv, int hd, int vd) {
+    chain_release();
+    chain_wait();
+    extern __shared__ __align__(16) float staged[];          // [warp][kRunTokens][hd]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kRunTokens;
+    const int q_w = n_heads * hd, k_w = n_kv * hd;
+    const int C = q_w + k_w + n_kv * vd;
+    const int n_turning = n_heads + n_kv, n_items = n_turning + n_kv;
+    constexpr int keep = TAPS - 1;
+    int before[kRunTokens], pos[kRunTokens], slot[kRunTokens];
+#pragma unroll
+    for (int tk = 0; tk < kRunTokens; ++tk) {
+        const int n = min(n0 + tk, N - 1);
+        const int b = token_seq[n];
+        before[tk] = n - cu_seqlens[b];
+        pos[tk] = positions[n];
+        slot[tk] = slots[b];
+    }
+    const int rhalf = rot >> 1;
+    for (int item = blockIdx.y * kFinishWarps + warp; item < n_items; item += gridDim.y * kFinishWarps) {
+        const bool is_v = item >= n_turning, is_q = item < n_heads;
+        if (!is_q && !kc) continue;
+        const int width = is_v ? vd : hd;
+        const int c0 = is_v ? q_w + k_w + (item - n_turning) * vd : item * hd;
+        float* x = staged + (size_t)warp * kRunTokens * hd;
+        for (int i = lane; i < width; i += 32) {
+            const int c = c0 + i;
+            float win[kRunTokens + keep], w[TAPS];
+#pragma unroll
+            for (int k = 0; k < kRunTokens + keep; ++k) {
+                const int row = n0 - keep + k;
+                win[k] = (row >= 0 && row < N) ? sums[(size_t)row * ld + c] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) w[j] = __ldg(conv_w + (size_t)j * C + c);
+            const float bc = bias ? __ldg(bias + c) : 0.f;
+#pragma unroll
+            for (int tk = 0; tk < kRunTokens; ++tk) {
+                float acc = 0.f;
+#pragma unroll
+                for (int j = 0; j < TAPS; ++j) {
+                    const int back = keep - j;
+                    if (pos[tk] - back < 0) continue;
+                    const float u = before[tk] - back >= 0 ? win[tk + j]
+                                                           : conv_state[((size_t)slot[tk] * keep + (keep + before[tk] - back)) * C + c];
+                    acc = fmaf(w[j], u + bc, acc);
+                }
+                x[tk * hd + i] = acc;
+            }
+        }
+        __syncwarp();
+        for (int tk = 0; tk < kRunTokens; ++tk) {
+            const int n = n0 + tk;
+            if (n >= N) break;
+            float* xt = x + tk * hd;
+            size_t page_off = 0;
+            if (kc) page_off = (size_t)block_table[(size_t)slot[tk] * table_stride + pos[tk] / kPageTokens] * page_stride;
+            if (is_v) {
+                T* dst = vc + page_off + ((size_t)(item - n_turning) * kPageTokens + (pos[tk] % kPageTokens)) * vd;
+                for (int i = lane; i < vd; i += 32) dst[i] = from_f32<T>(xt[i]);
+                continue;
+            }
+            const float* nw = is_q ? q_norm : k_norm;
+            if (nw) {
+                float sq = 0.f;
+                for (int i = lane; i < hd; i += 32) sq = fmaf(xt[i], xt[i], sq);
+                const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)hd + eps);
+                for (int i = lane; i < hd; i += 32) xt[i] = xt[i] * inv * __ldg(nw + i);
+                __syncwarp();
+            }
+            if (cos_sin) {
+                for (int i = lane; i < rhalf; i += 32) {
+                    const float2 cs = cos_sin[(size_t)n * rhalf + i];
+                    const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + rhalf;
+                    const float a = xt[ia], bb = xt[ib];
+                    xt[ia] = a * cs.x - bb * cs.y;
+                    xt[ib] = bb * cs.x + a * cs.y;
+                }
+                __syncwarp();
+            }
+            T* dst = is_q ? q_out + (size_t)n * ldq + (size_t)item * hd
+                          : kc + page_off + ((size_t)(item - n_heads) * kPageTokens + (pos[tk] % kPageTokens)) * hd;
+            if (hd % 2 == 0 && (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(T))) == 0) {
+                for (int i = lane * 2; i < hd; i += 64) store_pair(dst + i, xt[i], xt[i + 1]);
+            } else {
+                for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(xt[i]);
+            }
+        }
+        __syncwarp();                                        // before the warp's next head overwrites x
+    }
+}
 }  // namespace
 
 GTG_API int gtg_qkv_finish(int dtype, const float* sums, int ld, const float* bias, const float* cos_sin, int rot,
@@ -374,6 +483,28 @@ GTG_API int gtg_qkv_conv_finish(int dtype, const float* sums, int ld, const floa
     const int n_items = n_heads + 2 * n_kv;
     const dim3 grid(N, (n_items + kFinishWarps - 1) / kFinishWarps);
     if (grid.y > 65535) return kErrUnsupported;
+    // many tokens and two to four taps: a warp takes a head of four consecutive rows at a time
+    constexpr int kManyTokens = 64;
+    const size_t smem_run = smem * kRunTokens;
+    if (N >= kManyTokens && taps >= 2 && taps <= 4 && vd <= hd && smem_run <= 200 * 1024) {
+        const dim3 grid_run((N + kRunTokens - 1) / kRunTokens, grid.y);
+#define GTG_CONV_RUN(T, TAPS)                                                                                      \
+        do {                                                                                                       \
+            auto kernel = qkv_conv_finish_run_kernel<T, TAPS>;                                                     \
+            if (smem_run > 48 * 1024) {                                                                            \
+                const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_run); \
+                if (e != cudaSuccess) return (int)e;                                                               \
+            }                                                                                                      \
+            return launch_chained(kernel, grid_run, dim3(kFinishWarps * 32), smem_run, stream, sums, ld, bias, conv_w, \
+                                  conv_state, cu_seqlens, q_norm, k_norm, eps, (const float2*)cos_sin, rot, interleaved, \
+                                  (T*)q_out, ldq, (T*)kc, (T*)vc, page_stride, block_table, table_stride, token_seq,   \
+                                  slots, positions, N, n_heads, n_kv, hd, vd);                                      \
+        } while (0)
+        if (dtype == 0) { if (taps == 2) GTG_CONV_RUN(float, 2); if (taps == 3) GTG_CONV_RUN(float, 3); GTG_CONV_RUN(float, 4); }
+        if (dtype == 1) { if (taps == 2) GTG_CONV_RUN(bf16, 2); if (taps == 3) GTG_CONV_RUN(bf16, 3); GTG_CONV_RUN(bf16, 4); }
+#undef GTG_CONV_RUN
+        return kErrBadArgument;
+    }
 #define GTG_CONV_FINISH(T)                                                                                         \
     do {                                                                                                           \
         auto kernel = qkv_conv_finish_kernel<T>;                                                                   \

@@ -145,7 +145,7 @@ delta_scan_kernel(const float* __restrict__ qk, int ld_qk, const float* __restri
     for (int t0 = 0; t0 < n_rows; t0 += kTile, buffer ^= 1) {
         const int nt = min(kTile, n_rows - t0);
         if (t0 + kTile < n_rows) {
-            stage(buffer ^ 1, t0 + kTile);                   // the other buffer: its tile was used up before the barrier that ended the last round
+            stage(buffer ^ 1, t0 + kTile);                   // the other buffer: its tile was used up before the barrier that ended the last pass of this loop
             copy_async_wait<1>();
         } else {
             copy_async_wait<0>();
@@ -470,6 +470,10 @@ static int delta_split(int d) {
     return R;
 }
 
+// Measurements may fix the lanes that share a column (8, 16 or 32; 0: the launcher chooses).
+static int g_delta_lanes = 0;
+GTG_API void gtg_delta_scan_lanes(int lanes) { g_delta_lanes = lanes; }
+
 GTG_API int gtg_delta_scan_supports(int d, int dv) {
     return d > 0 && dv > 0 && d <= 32 * kRows && (size_t)2 * (3 * kTile * d + kTile * kFixedThreads + 2 * kTile) * 4 <= 200 * 1024;
 }
@@ -499,12 +503,17 @@ GTG_API int gtg_delta_scan(const float* qk, int ld_qk, const float* v, int ld_v,
     }
     const int wide16 = ld_qk % 4 == 0 && ld_decay % 4 == 0 && ((uintptr_t)qk % 16) == 0 && ((uintptr_t)decay % 16) == 0;
     if (wide16 && (d == 64 || d == 128 || d == 256)) {
-        // lanes a column: the fewest (fewest exchanges) that still give every scheduler about four warps
+        // lanes a column: the fewest (fewest exchanges, fewest reads of shared memory a column) that still give the
+        // device about seven warps a multiprocessor, not quite two a scheduler.  Measured at d = 128 with 2,048-token
+        // prompts: 2,048 columns 0.86 / 0.58 / 0.65 ms at 8 / 16 / 32 lanes, 4,096 columns 0.86 / 0.80 / 1.10,
+        // 8,192 columns 1.21 / 1.42 / 1.91: more warps hide a token's chain of dependent steps, but every warp
+        // reads the whole of q, k and g, and beyond some thousand warps shared memory is the limit.
         int device = 0, sms = 148;
         if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         const long long columns = (long long)n_seqs * n_heads * dv;
         int RT = d / kRows;
-        while (RT < 32 && columns * RT / 32 < 16LL * sms) RT *= 2;
+        while (RT < 32 && columns * RT / 32 < 27LL * sms / 4) RT *= 2;
+        if (g_delta_lanes >= d / kRows && g_delta_lanes <= 32 && (g_delta_lanes & (g_delta_lanes - 1)) == 0) RT = g_delta_lanes;
 #define GTG_FIXED(KR, R) launch_fixed<KR, R>(qk, ld_qk, v, ld_v, decay, ld_decay, beta, state, out, ld_out, cu_seqlens, slots, n_seqs, \
                                              n_heads, n_groups, dv, stream)
         if (d == 64) return RT == 4 ? GTG_FIXED(16, 4) : RT == 8 ? GTG_FIXED(8, 8) : RT == 16 ? GTG_FIXED(4, 16) : GTG_FIXED(2, 32);
