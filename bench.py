@@ -816,7 +816,7 @@ def run_design(args):
             state = torch.zeros(n_seqs, taps - 1, C, dtype=f32, device=dev)
             nq, nk, cs = rnd(hd, dtype=f32), rnd(hd, dtype=f32), rnd(n, hd // 4, 2, dtype=f32)
             q = torch.empty(n, heads * hd, dtype=bf, device=dev)
-            add(f"qkv_conv_finish ({tag})", n, timed(lambda: ops.qkv_conv_finish(sums, bias, cw, state, cu, nq, nk, 1e-5, cs, True, heads, n_kv, hd, hd, kv, q, seq, slots, pos)),
+            add(f"qkv_conv_finish ({tag})", n, timed(lambda: ops.qkv_conv_finish(sums, bias, cw, state, cu, nq, nk, 1e-5, cs, True, heads, n_kv, hd, hd, kv, q, seq, slots, pos, one_token_each=per == 1)),
                 n * C * (4 + 2))
             add(f"conv_state_update ({tag})", n, timed(lambda: ops.conv_state_update(sums[:, :C], state, cu, slots, n_seqs)), n_seqs * (taps - 1) * C * 8)
             qkv, cs2 = rnd(n, C), rnd(n, hd // 2, 2, dtype=f32)

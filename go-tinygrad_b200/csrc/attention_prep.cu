@@ -471,7 +471,7 @@ GTG_API int gtg_qkv_conv_finish(int dtype, const float* sums, int ld, const floa
                                 float eps, const float* cos_sin, int rot, int interleaved, void* q_out, int ldq,
                                 void* kc, void* vc, long long page_stride, const int* block_table, int table_stride,
                                 const int* token_seq, const int* slots, const int* positions, int N, int n_heads,
-                                int n_kv, int hd, int vd, cudaStream_t stream) {
+                                int n_kv, int hd, int vd, int one_token_each, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (n_heads <= 0 || n_kv < 0 || hd <= 0 || vd <= 0 || rot < 0 || (rot & 1) || rot > hd || taps < 1) return kErrBadArgument;
     if ((cos_sin != nullptr) != (rot > 0) || (kc == nullptr) != (vc == nullptr)) return kErrBadArgument;
@@ -486,7 +486,8 @@ GTG_API int gtg_qkv_conv_finish(int dtype, const float* sums, int ld, const floa
     // many tokens and two to four taps: a warp takes a head of four consecutive rows at a time
     constexpr int kManyTokens = 64;
     const size_t smem_run = smem * kRunTokens;
-    if (N >= kManyTokens && taps >= 2 && taps <= 4 && vd <= hd && smem_run <= 200 * 1024) {
+    // (not a step of one token a sequence: there neighbouring rows share nothing)
+    if (!one_token_each && N >= kManyTokens && taps >= 2 && taps <= 4 && vd <= hd && smem_run <= 200 * 1024) {
         const dim3 grid_run((N + kRunTokens - 1) / kRunTokens, grid.y);
 #define GTG_CONV_RUN(T, TAPS)                                                                                      \
         do {                                                                                                       \

@@ -59,7 +59,7 @@ _SIGNATURES = {
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                   _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I, _F, _P, _P]),
     "gtg_qkv_conv_finish": ("attention_prep", [_I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _F, _P, _I, _I, _P, _I, _P, _P, _L, _P, _I,
-                                               _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+                                               _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_delta_prepare": ("delta", [_P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P]),
     "gtg_delta_scan_supports": ("delta", [_I, _I]),
     "gtg_delta_scan": ("delta", [_P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
@@ -588,7 +588,7 @@ def qkv_conv_finish(sums: torch.Tensor, bias: Optional[torch.Tensor], conv_w: Op
                     conv_state: Optional[torch.Tensor], cu_seqlens, q_norm: Optional[torch.Tensor],
                     k_norm: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor], interleaved: bool,
                     n_heads: int, n_kv: int, head_dim: int, value_dim: int, kv, q_out: torch.Tensor,
-                    token_seq, slots, positions, store: bool = True) -> None:
+                    token_seq, slots, positions, store: bool = True, one_token_each: bool = False) -> None:
     """Between the fused projection and the attention, for mixers whose q, k and v pass a
     short causal convolution over time: of the float32 sums [N, >= q | k | v] (n_kv key and
     value heads; 0: queries only) add the bias [q | k | v], convolve every channel over the
@@ -597,7 +597,8 @@ def qkv_conv_finish(sums: torch.Tensor, bias: Optional[torch.Tensor], conv_w: Op
     head with q_norm / k_norm (float32 [head_dim]; None: no norm), rotate the head's first
     2 * cos_sin.shape[1] channels (2i with 2i+1 if `interleaved`, else i with i + half),
     write queries to q_out and, with `store`, keys and values to the cache.  The state is
-    not changed: `conv_state_update` over the same sums follows."""
+    not changed: `conv_state_update` over the same sums follows.  `one_token_each`: a decode
+    step (the form that shares a run of rows between neighbouring tokens is then not taken)."""
     _rows2d(sums, "qkv_conv_finish: sums"); _rows2d(q_out, "qkv_conv_finish: q_out")
     N = sums.shape[0]
     C = n_heads * head_dim + n_kv * (head_dim + value_dim)
@@ -635,7 +636,8 @@ def qkv_conv_finish(sums: torch.Tensor, bias: Optional[torch.Tensor], conv_w: Op
                                       _ptr(kv.k) if store else None, _ptr(kv.v) if store else None,
                                       kv.page_stride if store else 0, _ptr(kv.block_table) if store else None,
                                       kv.table_stride if store else 0, _ptr(token_seq), _ptr(slots), _ptr(positions),
-                                      N, n_heads, n_kv, head_dim, value_dim, _stream()), "qkv_conv_finish")
+                                      N, n_heads, n_kv, head_dim, value_dim, 1 if one_token_each else 0, _stream()),
+           "qkv_conv_finish")
 
 
 # ------------------------------------------------------------- the gated delta rule

@@ -230,7 +230,7 @@ class GQAttention(Mixer):
         ops.qkv_conv_finish(sums, self.bias, self.conv_w, state, ctx.cu_seqlens, self.q_norm_w, self.k_norm_w, self.norm_eps,
                             rotation, self.position.pairing == "interleaved", self.n_heads, self.n_kv if self.own_kv else 0,
                             self.head_dim, self.value_dim, kv, q, ctx.token_seq, ctx.slots, ctx.positions,
-                            store=cache.writes and self.own_kv)
+                            store=cache.writes and self.own_kv, one_token_each=ctx.is_decode)
         if state is not None:
             # the convolution has read what it needed of the old state: now the step's raw sums join it
             ops.conv_state_update(sums[:, : self.conv_channels], state, ctx.cu_seqlens, ctx.slots, ctx.n_seqs)
