@@ -855,26 +855,54 @@ GTG_API int gtg_add_bias(int dtype, const float* x, const float* b, void* out, i
     return kErrBadArgument;
 }
 
-// x[m,n] *= sigmoid(g[m,n]), the product evaluated in float: a gate on a mixer's heads.
-template <typename T>
-__global__ void sigmoid_gate_kernel(T* __restrict__ x, int ldx, const T* __restrict__ g, int ldg, int M, int N) {
+// x[m,n] *= sigmoid(g[m,n]), the product evaluated in float: a gate on a mixer's heads.  The logits g
+// are of x's type or float (a projection's sums).
+template <typename T, typename G>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, int ldx, const G* __restrict__ g, int ldg, int M, int N) {
     chain_release();
     chain_wait();
     const size_t total = (size_t)M * N;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t m = idx / N;
         const int n = (int)(idx % N);
-        const float gate = 1.0f / (1.0f + expf(-to_f32<T>(g[m * ldg + n])));
+        const float gate = 1.0f / (1.0f + expf(-to_f32<G>(g[m * ldg + n])));
         x[m * ldx + n] = from_f32<T>(to_f32<T>(x[m * ldx + n]) * gate);
     }
 }
 
-GTG_API int gtg_sigmoid_gate(int dtype, void* x, int ldx, const void* g, int ldg, int M, int N, cudaStream_t stream) {
+// The same for bfloat16 rows and float logits whose rows allow 16-byte accesses: eight channels a thread.
+__global__ void sigmoid_gate_bf16_f32_vec_kernel(bf16* __restrict__ x, int ldx, const float* __restrict__ g, int ldg, int M, int N8) {
+    chain_release();
+    chain_wait();
+    const size_t total = (size_t)M * N8;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = idx / N8;
+        const int c = (int)(idx % N8) * 8;
+        uint4 xv = *reinterpret_cast<const uint4*>(x + m * ldx + c);
+        const float4 g0 = *reinterpret_cast<const float4*>(g + m * ldg + c), g1 = *reinterpret_cast<const float4*>(g + m * ldg + c + 4);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        __nv_bfloat162* xh = reinterpret_cast<__nv_bfloat162*>(&xv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(xh[e]);
+            xh[e] = __floats2bfloat162_rn(f.x * (1.0f / (1.0f + expf(-gg[2 * e]))), f.y * (1.0f / (1.0f + expf(-gg[2 * e + 1]))));
+        }
+        *reinterpret_cast<uint4*>(x + m * ldx + c) = xv;
+    }
+}
+
+GTG_API int gtg_sigmoid_gate(int dtype, void* x, int ldx, const void* g, int ldg, int M, int N, int gate_f32, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
+    if (dtype == 1 && gate_f32 && N % 8 == 0 && ldx % 8 == 0 && ldg % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)g % 16) == 0) {
+        const size_t total8 = (size_t)M * (N / 8);
+        const unsigned blocks8 = (unsigned)((total8 + 255) / 256 > 148 * 16 ? 148 * 16 : (total8 + 255) / 256);
+        return launch_chained(sigmoid_gate_bf16_f32_vec_kernel, dim3(blocks8), dim3(256), 0, stream, (bf16*)x, ldx, (const float*)g, ldg, M, N / 8);
+    }
     const size_t total = (size_t)M * N;
     const unsigned blocks = (unsigned)((total + 255) / 256 > 8192 ? 8192 : (total + 255) / 256);
-    if (dtype == 0) return launch_chained(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, ldx, (const float*)g, ldg, M, N);
-    if (dtype == 1) return launch_chained(sigmoid_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ldx, (const bf16*)g, ldg, M, N);
+    if (dtype == 0) return launch_chained(sigmoid_gate_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (float*)x, ldx, (const float*)g, ldg, M, N);
+    if (dtype == 1 && gate_f32) return launch_chained(sigmoid_gate_kernel<bf16, float>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ldx, (const float*)g, ldg, M, N);
+    if (dtype == 1) return launch_chained(sigmoid_gate_kernel<bf16, bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ldx, (const bf16*)g, ldg, M, N);
     return kErrBadArgument;
 }
 

@@ -68,7 +68,7 @@ _SIGNATURES = {
     "gtg_round_rows": ("elementwise", [_I, _P, _P, _L, _P]),
     "gtg_swiglu_bias": ("elementwise", [_I, _P, _P, _P, _P, _I, _I, _I, _P]),
     "gtg_add_bias": ("elementwise", [_I, _P, _P, _P, _I, _I, _P]),
-    "gtg_sigmoid_gate": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _P]),
+    "gtg_sigmoid_gate": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_simt_batched": ("gemm_f32", [_I, _P, _I, _L, _P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_grouped": ("gemm_bf16_grouped", [_P, _I, _L, _P, _I, _P, _I, _L, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I,
                                                     _I, _P, _I, _L, _P]),
@@ -577,11 +577,11 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
-    """x *= sigmoid(gate) in place, evaluated in float."""
+    """x *= sigmoid(gate) in place, evaluated in float; the logits are of x's dtype or float32."""
     _rows2d(x, "sigmoid_gate: x"); _rows2d(gate, "sigmoid_gate: gate")
-    _need(x.shape == gate.shape and x.dtype == gate.dtype, "sigmoid_gate: x and gate must agree in shape and dtype")
+    _need(x.shape == gate.shape and gate.dtype in (x.dtype, torch.float32), "sigmoid_gate: x and gate must agree in shape, gate of x's dtype or float32")
     _check(_fn("gtg_sigmoid_gate")(_dt(x), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0), x.shape[0], x.shape[1],
-                                   _stream()), "sigmoid_gate")
+                                   1 if gate.dtype == torch.float32 else 0, _stream()), "sigmoid_gate")
 
 
 def qkv_conv_finish(sums: torch.Tensor, bias: Optional[torch.Tensor], conv_w: Optional[torch.Tensor],
@@ -1100,8 +1100,13 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kv, ctx, n_heads: int,
     rows [N, n_heads * value width] whose sigmoids multiply the output channel by channel."""
     if (q.dtype == torch.bfloat16 and not ctx.is_decode and kv.value_dim == kv.head_dim and attention_tcgen05_supports(kv)
             and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
+        # the logits' sigmoids multiply the output in a kernel of their own here: in this kernel's epilogue a thread
+        # holds a query's row and reads its 64 or 128 logits alone, which cost the kernel 37 us of 94 at 2,048 tokens
+        # against 10 us for the pass over rows
         attention_prefill_tcgen05(q, out, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, ctx.n_seqs, ctx.max_q_len, n_heads, scale,
-                                  window, chunk, gate, softcap=softcap, gate_logits=gate_logits)
+                                  window, chunk, gate, softcap=softcap)
+        if gate_logits is not None:
+            sigmoid_gate(out[:, : n_heads * kv.value_dim], gate_logits)
         return
     if q.dtype == torch.bfloat16 and attention_masked_supports(kv) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and scale > 0:
         splits = int(_fn("gtg_attention_masked_splits")(ctx.n_seqs, ctx.max_q_len, n_heads, kv.n_kv_heads, ctx.max_kv_len,

@@ -204,16 +204,17 @@ def short(weights, prefix):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("taps,window_a,window_b", [(3, 1, 2), (2, 5, 70), (5, 64, 65), (None, 2, None), (4, None, 3)])
-def test_attention_with_convolved_projections_short_windows_and_borrowed_keys(dtype, taps, window_a, window_b):
+@pytest.mark.parametrize("taps,window_a,window_b,dim,vdim", [(3, 1, 2, 12, 6), (2, 5, 70, 12, 6), (5, 64, 65, 12, 6), (None, 2, None, 12, 6),
+                                                             (4, None, 3, 12, 6), (3, 40, 7, 8, 20), (4, 3, None, 16, 40)])
+def test_attention_with_convolved_projections_short_windows_and_borrowed_keys(dtype, taps, window_a, window_b, dim, vdim):
     """Random weights, windows of 1, 2, 3 and 5 keys (every key weighs, so a window or a tap one
     off shows everywhere), a second mixer that reads the first one's keys and values through queries,
     taps, window and cap of its own; prompts against portions down to two tokens and single tokens."""
     rng = np.random.default_rng(7)
     hidden, T = 40, 150
     rot = {"dims": 6, "base": 30.0, "scaling": SCALING}
-    ma = attention(4, 2, 12, 6, 0.4, conv=taps, window=window_a, rot=rot, softcap=3.0)
-    mb = attention(4, 2, 12, 6, 0.3, conv=2, window=window_b, rot=rot, kv_from=0)
+    ma = attention(4, 2, dim, vdim, 0.4, conv=taps, window=window_a, rot=rot, softcap=3.0)        # values narrower and wider than keys
+    mb = attention(4, 2, dim, vdim, 0.3, conv=2, window=window_b, rot=rot, kv_from=0)
     weights = random_weights(rng, {**attention_shapes("l0.mix.", ma, hidden), **attention_shapes("l1.mix.", mb, hidden, own=False)})
     for name in ("l0.mix.q.b", "l0.mix.k.b", "l0.mix.v.b", "l1.mix.q.b"):
         weights[name] = weights[name] * 3          # biases large enough that one added after the convolution, or to the zeros before the start, shows
